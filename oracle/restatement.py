@@ -273,11 +273,12 @@ def layer_norm_heads(x, weight, bias, eps=1e-5):
 
 def module_forward(params: dict, x: torch.Tensor, xpos: Optional[torch.Tensor], num_heads: int,
                    block_size: int = 4, topk: int = 32, rope_base: float = 100.0,
-                   return_aux: bool = False):
+                   return_aux: bool = False, idx_override: Optional[torch.Tensor] = None):
     """Restatement of ``SparseFlashAttentionRope.forward`` (sparse_attention.py:90-141).
 
     ``params`` uses the module's state-dict keys (``qkv.weight`` ... ``gate.0.bias``).
-    Runs in the dtype of ``x`` (fp32 for the oracle)."""
+    Runs in the dtype of ``x`` (fp32 for the oracle).  ``idx_override`` replaces the selected
+    block table (used to compare a bf16 run, whose near-tie selections may differ, on equal terms)."""
     B, T, C = x.shape
     H = num_heads
     d = C // H
@@ -294,6 +295,8 @@ def module_forward(params: dict, x: torch.Tensor, xpos: Optional[torch.Tensor], 
         pc = block_positions(xpos, Bs)
         q_c, k_c = rope2d(q_c, pc, rope_base), rope2d(k_c, pc, rope_base)
     o_c, _, idx = cmp_attn_topk(q_c, k_c, v_c, topk)
+    if idx_override is not None:
+        idx = idx_override
     qkv_full = qkv.reshape(B, T, 3, H, d).transpose(1, 3)
     q, k, v = qkv_full[:, :, 0], qkv_full[:, :, 1], qkv_full[:, :, 2]
     if has_norm:

@@ -1,0 +1,143 @@
+"""Drop-in replacement for the reference's global-attention module.
+
+``SparseFlashAttentionRope`` keeps the constructor signature, sub-module names (``qkv``, ``proj``,
+``q_norm``, ``k_norm``, ``gate`` = Sequential(Linear, Sigmoid)), attributes and ``forward(x,
+attn_bias=None, xpos=None)`` of pi3/models/layers/sparse_attention.py:60-141, so a checkpoint of
+the reference loads unchanged and ``BlockRope(attn_class=SparseFlashAttentionRope)`` works
+(pi3/models/layers/block.py:282-312).  The projections, LayerNorms and the rotary embedding stay
+PyTorch host code; pooling, the compression attention with its top-k selection, the selection
+attention and the gated merge run in the CUDA library (speed3r_b200.ops).
+
+The reference's literals (pooling 16/16, top-k 32) are keyword arguments here with the same
+defaults.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor, nn
+
+from . import ops
+
+
+class RoPE2D(nn.Module):
+    """2-D rotary embedding with the arithmetic of pi3/models/layers/pos_embed.py:112-159 (the
+    angle table is rounded to the activation dtype before cos/sin).  Unlike the reference it does
+    not read ``positions.max()`` back on every call: the table length is cached per position
+    tensor."""
+
+    def __init__(self, freq: float = 100.0, F0: float = 1.0):
+        super().__init__()
+        self.base = freq
+        self.F0 = F0
+        self._tables = {}
+        self._maxpos = {}
+
+    def _cos_sin(self, D, seq_len, device, dtype):
+        key = (D, seq_len, device, dtype)
+        if key not in self._tables:
+            inv_freq = 1.0 / (self.base ** (torch.arange(0, D, 2).float().to(device) / D))
+            t = torch.arange(seq_len, device=device, dtype=inv_freq.dtype)
+            freqs = torch.einsum("i,j->ij", t, inv_freq).to(dtype)
+            freqs = torch.cat((freqs, freqs), dim=-1)
+            self._tables[key] = (freqs.cos(), freqs.sin())
+        return self._tables[key]
+
+    def _seq_len(self, positions: Tensor) -> int:
+        key = (positions.data_ptr(), tuple(positions.shape), positions._version, positions.device)
+        if key not in self._maxpos:
+            if len(self._maxpos) > 64:
+                self._maxpos.clear()
+            self._maxpos[key] = int(positions.max()) + 1
+        return self._maxpos[key]
+
+    @staticmethod
+    def _rope1d(tokens, pos1d, cos, sin):
+        cos = torch.nn.functional.embedding(pos1d, cos)[:, None, :, :]
+        sin = torch.nn.functional.embedding(pos1d, sin)[:, None, :, :]
+        x1, x2 = tokens[..., : tokens.shape[-1] // 2], tokens[..., tokens.shape[-1] // 2:]
+        return tokens * cos + torch.cat((-x2, x1), dim=-1) * sin
+
+    def forward(self, tokens: Tensor, positions: Tensor, seq_len: Optional[int] = None) -> Tensor:
+        D = tokens.size(3) // 2
+        if seq_len is None:
+            seq_len = self._seq_len(positions)
+        cos, sin = self._cos_sin(D, seq_len, tokens.device, tokens.dtype)
+        y, x = tokens.chunk(2, dim=-1)
+        y = self._rope1d(y, positions[:, :, 0], cos, sin)
+        x = self._rope1d(x, positions[:, :, 1], cos, sin)
+        return torch.cat((y, x), dim=-1)
+
+
+class SparseFlashAttentionRope(nn.Module):
+    def __init__(
+        self,
+        dim: int,
+        num_heads: int = 16,
+        qkv_bias: bool = False,
+        proj_bias: bool = True,
+        attn_drop: float = 0.0,
+        proj_drop: float = 0.0,
+        qk_norm: bool = False,
+        norm_layer: nn.Module = nn.LayerNorm,
+        rope=None,
+        block_size: int = 4,
+        topk: int = 32,
+    ) -> None:
+        super().__init__()
+        self.num_heads = num_heads
+        head_dim = dim // num_heads
+        self.scale = head_dim ** -0.5
+        self.qkv = nn.Linear(dim, dim * 3, bias=qkv_bias)
+        self.attn_drop = nn.Dropout(attn_drop)
+        self.proj = nn.Linear(dim, dim, bias=proj_bias)
+        self.proj_drop = nn.Dropout(proj_drop)
+        self.q_norm = norm_layer(head_dim) if qk_norm else nn.Identity()
+        self.k_norm = norm_layer(head_dim) if qk_norm else nn.Identity()
+        self.rope = rope
+        gate_linear = nn.Linear(dim, num_heads * 2, bias=True)
+        nn.init.zeros_(gate_linear.weight)
+        gate_linear.bias.data.copy_(torch.tensor([-1.0, 1.0]).repeat(num_heads))
+        self.gate = nn.Sequential(gate_linear, nn.Sigmoid())
+        self.block_size = block_size
+        self.topk = topk
+        self.record_idx = False      # debugging aid: keep the last selected-block table in .last_idx
+        self.last_idx = None
+
+    def forward(self, x: Tensor, attn_bias=None, xpos: Optional[Tensor] = None) -> Tensor:
+        B, N, C = x.shape
+        H = self.num_heads
+        d = C // H
+        Bs = self.block_size ** 2
+        qkv = self.qkv(x)
+        gate = self.gate(x).view(B, N, H, 2).permute(0, 2, 1, 3)          # [B,H,N,2] view, no copy
+        if qkv.dtype != torch.bfloat16:
+            raise RuntimeError("SparseFlashAttentionRope runs in bf16 (use torch.autocast(dtype=torch.bfloat16)); "
+                               f"got {qkv.dtype}")
+        gate = gate.to(qkv.dtype)
+        qkv5 = qkv.view(B, N, 3, H, d)
+        q_t, k_t, v_t = (qkv5[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # [B,H,N,d] views of the projection
+
+        # compression branch: pool raw q,k,v, then norm + rope with the block's mean position
+        q_c, k_c, v_c = (ops.pool_tokens(t, Bs, Bs) for t in (q_t, k_t, v_t))
+        q_c, k_c = self.q_norm(q_c).to(v_c.dtype), self.k_norm(k_c).to(v_c.dtype)
+        rope_kw = {}
+        if xpos is not None and isinstance(self.rope, RoPE2D):
+            rope_kw = dict(seq_len=self.rope._seq_len(xpos))     # one table for token and block positions
+        if xpos is not None:
+            xpos_c = xpos.view(B, N // Bs, Bs, 2).float().mean(dim=2).int()
+            q_c = self.rope(q_c, xpos_c, **rope_kw)
+            k_c = self.rope(k_c, xpos_c, **rope_kw)
+        o_c, idx = ops.flash_attn_topk_func(q_c, k_c, v_c, self.topk)
+        if self.record_idx:
+            self.last_idx = idx.detach()
+
+        # selection branch at token level, gated merge fused into its epilogue
+        q, k = self.q_norm(q_t).to(qkv.dtype), self.k_norm(k_t).to(qkv.dtype)
+        if xpos is not None:
+            q = self.rope(q, xpos, **rope_kw)
+            k = self.rope(k, xpos, **rope_kw)
+        y = ops.sel_attn_merge(q.contiguous(), k.contiguous(), v_t.contiguous(), idx, gate, o_c, Bs)
+        y = self.proj(y)
+        return self.proj_drop(y)

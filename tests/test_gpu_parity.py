@@ -1,0 +1,387 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle on the same seeded,
+bf16-rounded inputs, plus the golden fixtures made from the reference's own kernels."""
+import math
+
+import pytest
+import torch
+
+from conftest import golden
+from _util import assert_bf16_close, assert_idx_match, bf16_round
+from oracle import restatement as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _status_clean():
+    from speed3r_b200 import _lib
+    _lib.load()
+    _lib.device_status(clear=True)
+    yield
+    assert _lib.device_status(clear=True) == 0, "a kernel reported a device-side status (timeout / bad index)"
+
+
+def dev(t, dtype=torch.bfloat16):
+    return t.to(DEV, dtype).contiguous()
+
+
+def randn(seed, *shape):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed))
+
+
+# ------------------------------------------------------------------------------------------ pooling
+@pytest.mark.parametrize("B,H,T,kernel,stride", [(1, 2, 256, 16, 16), (2, 3, 1041, 32, 16), (1, 16, 2048, 16, 16),
+                                                 (1, 1, 100, 16, 16), (1, 2, 333, 32, 32)])
+def test_pool_fwd_bwd(B, H, T, kernel, stride):
+    from speed3r_b200 import ops
+    x, = bf16_round(randn(1, B, H, T, 64))
+    ref = R.pool_tokens(x, kernel, stride)
+    xg = dev(x).requires_grad_(True)
+    out = ops.pool_tokens(xg, kernel, stride)
+    assert_bf16_close(out, ref, "pool fwd", max_abs=4e-3, mean_abs=1e-3)
+    g, = bf16_round(randn(2, *ref.shape))
+    out.backward(dev(g))
+    xr = x.clone().requires_grad_(True)
+    R.pool_tokens(xr, kernel, stride).backward(g)
+    assert_bf16_close(xg.grad, xr.grad, "pool bwd", max_abs=4e-3, mean_abs=1e-3)
+
+
+def test_pool_packed_qkv_view():
+    """Pooling reads the packed projection [B,T,3,H,d] in place through strides."""
+    from speed3r_b200 import ops
+    B, T, H, d = 2, 320, 4, 64
+    qkv, = bf16_round(randn(3, B, T, 3 * H * d))
+    ref = R.pool_qkv(qkv, H, 16, 16)
+    qg = dev(qkv).view(B, T, 3, H, d)
+    for i in range(3):
+        out = ops.pool_tokens(qg[:, :, i].permute(0, 2, 1, 3), 16, 16)
+        assert_bf16_close(out, ref[i], f"pool packed {i}", max_abs=4e-3, mean_abs=1e-3)
+
+
+# ------------------------------------------------------------------- compression attention + top-k
+def _cmp_case(q, k, v, topk, exact=False, variant=0, what=""):
+    from speed3r_b200 import ops, _lib
+    q, k, v = bf16_round(q, k, v)
+    o_ref, lse_ref, idx_ref = R.cmp_attn_topk(q, k, v, topk)
+    S = torch.matmul(q, k.transpose(-1, -2))
+    _lib.load().s3r_debug_set_cmp_variant(variant)
+    try:
+        o, lse, idx = ops._cmp_fwd(dev(q), dev(k), dev(v), topk, 1.0 / math.sqrt(q.shape[-1]))
+        torch.cuda.synchronize()
+    finally:
+        _lib.load().s3r_debug_set_cmp_variant(0)
+    assert_idx_match(idx, idx_ref, S, what + " idx", exact=exact)
+    assert_bf16_close(o, o_ref, what + " o_c")
+    assert_bf16_close(lse, lse_ref, what + " lse", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("name", ["cmp_basic", "cmp_ragged", "cmp_rect", "cmp_short", "cmp_ties"])
+def test_cmp_attn_topk_golden(name, variant):
+    g = golden(name)
+    _cmp_case(g["q"], g["k"], g["v"], int(g["topk"]), exact=(name in ("cmp_ties", "cmp_short")), variant=variant,
+              what=f"{name}/v{variant}")
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("B,H,Nq,Nc,topk", [(1, 4, 1000, 1000, 32), (2, 2, 300, 2500, 16), (1, 2, 257, 129, 32),
+                                            (1, 1, 4032, 4032, 32), (1, 2, 5, 40, 8)])
+def test_cmp_attn_topk_seeded(B, H, Nq, Nc, topk, variant):
+    q, k, v = randn(11, B, H, Nq, 64), randn(12, B, H, Nc, 64), randn(13, B, H, Nc, 64)
+    _cmp_case(q, k, v, topk, variant=variant, what=f"seeded {Nq}x{Nc}/v{variant}")
+
+
+def test_cmp_attn_large_logits_and_rescale():
+    """Row maxima that grow along the key axis force the lazy O rescale path."""
+    B, H, N = 1, 2, 1024
+    q, k, v = randn(21, B, H, N, 64), randn(22, B, H, N, 64), randn(23, B, H, N, 64)
+    k = k * torch.linspace(0.2, 3.0, N).view(1, 1, N, 1)
+    _cmp_case(q * 1.5, k, v, 32, what="rescale")
+
+
+def test_cmp_attn_matches_device_check_at_scale():
+    """100 views x 1008 tokens (Nc = 6300), all 16 heads: tensor-core kernel vs the SIMT restatement."""
+    from speed3r_b200 import ops
+    B, H, N = 1, 16, 6300
+    g = torch.Generator(device=DEV).manual_seed(5)
+    q, k, v = (torch.nn.functional.layer_norm(torch.randn(B, H, N, 64, device=DEV, generator=g), (64,)).bfloat16()
+               for _ in range(3))
+    o, lse, idx = ops._cmp_fwd(q, k, v, 32, 0.125)
+    o2, lse2, idx2 = ops.check_cmp_attn_topk(q, k, v, 32, 0.125)
+    torch.cuda.synchronize()
+    assert_bf16_close(o, o2, "o_c vs device check")
+    assert_bf16_close(lse, lse2, "lse vs device check", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
+    frac = (idx != idx2).float().mean().item()
+    assert frac < 2e-3, f"{frac:.2e} of index entries differ from the device check"
+    for h in (0, 7, 15):            # tie check of the differing entries on a few heads
+        S = torch.matmul(q[0, h].float(), k[0, h].float().t()).cpu()
+        assert_idx_match(idx[0, h], idx2[0, h], S, f"scale idx head {h}")
+
+
+# ---------------------------------------------------------------------------- selection attention
+def _rand_idx(seed, B, H, nqb, nkb, K):
+    g = torch.Generator().manual_seed(seed)
+    return torch.stack([torch.stack([torch.stack([
+        (torch.randperm(nkb, generator=g)[:K] if nkb >= K else torch.randint(0, nkb, (K,), generator=g))
+        for _ in range(nqb)]) for _ in range(H)]) for _ in range(B)]).int()
+
+
+@pytest.mark.parametrize("name", ["sel_basic", "sel_k32", "sel_dup", "sel_neg", "sel_bs64"])
+def test_sel_attn_golden(name):
+    from speed3r_b200 import ops
+    g = golden(name)
+    q, k, v = bf16_round(g["q"], g["k"], g["v"])
+    o_ref, lse_ref = R.sel_attn(q, k, v, g["idx"], int(g["block"]))
+    o = ops.topk_blocksparse_attention(dev(q), dev(k), dev(v), g["idx"].to(DEV), int(g["block"]))
+    assert_bf16_close(o, o_ref, name + " o_s")
+    # the fixture itself (fp32 inputs) is within bf16 input-rounding distance as well
+    assert_bf16_close(o, g["o"], name + " o_s vs fixture", max_abs=6e-2, mean_abs=6e-3)
+
+
+@pytest.mark.parametrize("B,H,T,Bs,K", [(1, 2, 1008, 16, 32), (2, 2, 1041, 16, 32), (1, 3, 1041, 64, 16),
+                                        (1, 2, 800, 32, 8), (1, 1, 48, 16, 32), (1, 2, 2048, 16, 33)])
+def test_sel_attn_seeded_fwd_bwd(B, H, T, Bs, K):
+    from speed3r_b200 import ops
+    q, k, v = bf16_round(randn(31, B, H, T, 64), randn(32, B, H, T, 64), randn(33, B, H, T, 64))
+    nb = (T + Bs - 1) // Bs
+    idx = _rand_idx(34, B, H, nb, nb, K)
+    idx[:, :, 0, 0] = nb - 1                   # the partial last block, when T % Bs != 0
+    idx[:, :, -1, 1] = nb - 1
+    if K >= 4:
+        idx[:, :, 1, 2] = -1                   # skipped
+        idx[:, :, 1, 3] = nb + 5               # out of range: skipped
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    o_ref, lse_ref = R.sel_attn(qr, kr, vr, idx, Bs)
+    qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
+    o = ops.topk_blocksparse_attention(qg, kg, vg, idx.to(DEV), Bs)
+    assert_bf16_close(o, o_ref, "o_s")
+    o_chk, lse_chk = ops.check_sel_attn(qg.detach(), kg.detach(), vg.detach(), idx.to(DEV), Bs)
+    assert_bf16_close(o_chk, o_ref, "device check o_s")
+    assert_bf16_close(lse_chk, lse_ref, "device check lse", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
+    do, = bf16_round(randn(35, B, H, T, 64))
+    o_ref.backward(do)
+    o.backward(dev(do))
+    assert_bf16_close(qg.grad, qr.grad, "dq")
+    assert_bf16_close(kg.grad, kr.grad, "dk")
+    assert_bf16_close(vg.grad, vr.grad, "dv")
+
+
+def test_sel_attn_merge_fused_fwd_bwd():
+    from speed3r_b200 import ops
+    B, H, T, Bs, K = 2, 4, 656, 16, 32
+    q, k, v = bf16_round(randn(41, B, H, T, 64), randn(42, B, H, T, 64), randn(43, B, H, T, 64))
+    nb = T // Bs
+    idx = _rand_idx(44, B, H, nb, nb, K)
+    gate_flat, = bf16_round(torch.sigmoid(randn(45, B, T, 2 * H)))
+    o_c, = bf16_round(randn(46, B, H, nb, 64))
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, gate_flat, o_c)]
+    qr, kr, vr, gr, ocr = leaves
+    o_s_ref, _ = R.sel_attn(qr, kr, vr, idx, Bs)
+    y_ref = R.gated_merge(gr.view(B, T, H, 2).permute(0, 2, 1, 3), ocr, o_s_ref, Bs)
+    gl = [dev(t).requires_grad_(True) for t in (q, k, v, gate_flat, o_c)]
+    qg, kg, vg, gg, ocg = gl
+    y = ops.sel_attn_merge(qg, kg, vg, idx.to(DEV), gg.view(B, T, H, 2).permute(0, 2, 1, 3), ocg, Bs)
+    assert_bf16_close(y, y_ref, "merged y")
+    dy, = bf16_round(randn(47, B, T, H * 64))
+    y_ref.backward(dy)
+    y.backward(dev(dy))
+    for name, a, b in zip(("dq", "dk", "dv", "dgate", "do_c"), gl, leaves):
+        assert_bf16_close(a.grad, b.grad, name)
+
+
+def test_sel_attn_chunked_kv_matches_dense():
+    """K/V stored as sequence chunks (the layout an all-gather leaves) give identical results."""
+    from speed3r_b200 import ops
+    B, H, T, Bs, K, G = 1, 2, 1024, 16, 32, 4
+    g = torch.Generator(device=DEV).manual_seed(7)
+    q, k, v = (torch.randn(B, H, T, 64, device=DEV, generator=g).bfloat16() for _ in range(3))
+    idx = _rand_idx(51, B, H, T // Bs, T // Bs, K).to(DEV)
+    o_d, lse_d, _ = ops._sel_fwd(q, k, v, idx, None, None, Bs, 0.125, True, True, 1)
+    kc = k.view(B, H, G, T // G, 64).permute(2, 0, 1, 3, 4).contiguous()
+    vc = v.view(B, H, G, T // G, 64).permute(2, 0, 1, 3, 4).contiguous()
+    o_c, lse_c, _ = ops._sel_fwd(q, kc, vc, idx, None, None, Bs, 0.125, True, True, G)
+    assert torch.equal(o_d, o_c) and torch.equal(lse_d, lse_c)
+
+
+def test_sel_attn_deterministic():
+    from speed3r_b200 import ops
+    B, H, T, Bs, K = 1, 4, 2048, 16, 32
+    g = torch.Generator(device=DEV).manual_seed(9)
+    q, k, v, do = (torch.randn(B, H, T, 64, device=DEV, generator=g).bfloat16() for _ in range(4))
+    idx = _rand_idx(52, B, H, T // Bs, T // Bs, K).to(DEV)
+    outs = []
+    for _ in range(2):
+        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = ops.topk_blocksparse_attention(qg, kg, vg, idx, Bs)
+        o.backward(do)
+        outs.append((o.detach(), qg.grad, kg.grad, vg.grad))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b), "two runs on identical inputs differ"
+
+
+# ----------------------------------------------------------------------------------- CSR, backward
+@pytest.mark.parametrize("B,H,Nq,K,Nkb", [(1, 2, 64, 8, 64), (2, 3, 100, 32, 100), (1, 1, 16, 32, 16)])
+def test_key_csr_matches_oracle(B, H, Nq, K, Nkb):
+    from speed3r_b200 import ops
+    idx = _rand_idx(61, B, H, Nq, Nkb, K)
+    idx[:, :, 0, 0] = -1
+    idx[:, :, 1, 1] = Nkb + 3
+    if Nkb < K:
+        idx[..., K // 2:] = Nkb - 1
+    offs_ref, qids_ref = R.key_centric_csr(idx, Nkb)
+    offs, qids = ops.build_key_csr(idx.to(DEV), Nkb)
+    assert torch.equal(offs.cpu(), offs_ref)
+    n = qids_ref.shape[-1]
+    for b in range(B):
+        for h in range(H):
+            tot = int(offs_ref[b, h, -1])
+            assert torch.equal(qids[b, h, :tot].cpu(), qids_ref[b, h, :tot])
+
+
+@pytest.mark.parametrize("name", ["cmp_basic", "cmp_ragged"])
+def test_cmp_attn_backward_golden(name):
+    from speed3r_b200 import ops
+    g = golden(name)
+    q, k, v, do = bf16_round(g["q"], g["k"], g["v"], g["do"])
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    o_ref, _, _ = R.cmp_attn_topk(qr, kr, vr, int(g["topk"]))
+    o_ref.backward(do)
+    qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
+    o, idx = ops.flash_attn_topk_func(qg, kg, vg, int(g["topk"]))
+    o.backward(dev(do))
+    assert_bf16_close(qg.grad, qr.grad, "dq_c")
+    assert_bf16_close(kg.grad, kr.grad, "dk_c")
+    assert_bf16_close(vg.grad, vr.grad, "dv_c")
+
+
+def test_cmp_attn_backward_seeded_rect():
+    from speed3r_b200 import ops
+    B, H, Nq, Nc = 2, 2, 203, 391
+    q, k, v, do = bf16_round(randn(71, B, H, Nq, 64), randn(72, B, H, Nc, 64), randn(73, B, H, Nc, 64),
+                             randn(74, B, H, Nq, 64))
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    R.cmp_attn_topk(qr, kr, vr, 16)[0].backward(do)
+    qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
+    ops.flash_attn_topk_func(qg, kg, vg, 16)[0].backward(dev(do))
+    assert_bf16_close(qg.grad, qr.grad, "dq_c")
+    assert_bf16_close(kg.grad, kr.grad, "dk_c")
+    assert_bf16_close(vg.grad, vr.grad, "dv_c")
+
+
+@pytest.mark.parametrize("name", ["sel_basic", "sel_k32", "sel_dup", "sel_bs64"])
+def test_sel_attn_backward_golden(name):
+    from speed3r_b200 import ops
+    g = golden(name)
+    q, k, v, do = bf16_round(g["q"], g["k"], g["v"], g["do"])
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    R.sel_attn(qr, kr, vr, g["idx"], int(g["block"]))[0].backward(do)
+    qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
+    ops.topk_blocksparse_attention(qg, kg, vg, g["idx"].to(DEV), int(g["block"])).backward(dev(do))
+    assert_bf16_close(qg.grad, qr.grad, name + " dq")
+    assert_bf16_close(kg.grad, kr.grad, name + " dk")
+    assert_bf16_close(vg.grad, vr.grad, name + " dv")
+
+
+# ------------------------------------------------------------------------ whole op / whole module
+def test_cfg1_op_forward():
+    """BASELINE config 1: B=1, T=2048 (8 views x 256), 16 heads, d=64, seed 0, 16/16/16/32."""
+    from speed3r_b200 import ops
+    torch.manual_seed(0)
+    B, H, T, d, Bs, K = 1, 16, 2048, 64, 16, 32
+    q, k, v = torch.randn(B, H, T, d), torch.randn(B, H, T, d), torch.randn(B, H, T, d)
+    gate = torch.sigmoid(torch.randn(B, H, T, 2))
+    q, k, v, gate = bf16_round(q, k, v, gate)
+    # oracle on the bf16-rounded inputs, with pooled tensors rounded to bf16 as the kernels see them
+    q_c, k_c, v_c = bf16_round(*(R.pool_tokens(t, Bs, Bs) for t in (q, k, v)))
+    qg, kg, vg, gg = dev(q), dev(k), dev(v), dev(gate)
+    qc, kc, vc = (ops.pool_tokens(t, Bs, Bs) for t in (qg, kg, vg))
+    for a, b in zip((qc, kc, vc), (q_c, k_c, v_c)):
+        assert_bf16_close(a, b, "cfg1 pooled", max_abs=4e-3, mean_abs=5e-4)
+    # from here on the oracle sees exactly the pooled tensors the kernels see
+    q_c, k_c, v_c = (t.cpu().float() for t in (qc, kc, vc))
+    o_c_ref, _, idx_ref = R.cmp_attn_topk(q_c, k_c, v_c, K)
+    o_c, idx = ops.flash_attn_topk_func(qc, kc, vc, K)
+    assert_idx_match(idx, idx_ref, torch.matmul(q_c, k_c.transpose(-1, -2)), "cfg1 idx")
+    assert_bf16_close(o_c, o_c_ref, "cfg1 o_c")
+    y = ops.sel_attn_merge(qg, kg, vg, idx, gg, o_c, Bs)
+    o_s_ref, _ = R.sel_attn(q, k, v, idx.cpu(), Bs)
+    y_ref = R.gated_merge(gate, o_c_ref, o_s_ref, Bs)
+    assert_bf16_close(y, y_ref, "cfg1 y")
+
+
+def _module_pair(g, backward=False):
+    import speed3r_b200
+    heads = int(g["heads"])
+    dim = g["x"].shape[-1]
+    m = speed3r_b200.SparseFlashAttentionRope(dim, num_heads=heads, qkv_bias=True, proj_bias=True, qk_norm=True,
+                                              rope=speed3r_b200.RoPE2D(100.0))
+    sd = {k[len("param."):]: v for k, v in g.items() if k.startswith("param.")}
+    m.load_state_dict(sd, strict=True)
+    return m.to(DEV), sd, heads
+
+
+def test_module_forward_golden():
+    """Whole module in bf16 autocast against the fp32 oracle (itself pinned to the reference's
+    output for this fixture).  bf16 noise can flip near-tie selections, so the oracle is given the
+    table the GPU selected; the agreement of that table with the fp32 selection is checked apart."""
+    g = golden("module_fwd")
+    m, sd, heads = _module_pair(g)
+    m.record_idx = True
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(g["x"].to(DEV), xpos=g["xpos"].to(DEV))
+    idx = m.last_idx.cpu()
+    y_ref, aux = R.module_forward(sd, g["x"], g["xpos"], heads, return_aux=True, idx_override=idx)
+    # three bf16 GEMMs, LayerNorm and RoPE in bf16 against fp32: looser than the op-level bound
+    assert_bf16_close(y, y_ref, "module y", max_abs=6e-2, mean_abs=8e-3)
+    _, aux0 = R.module_forward(sd, g["x"], g["xpos"], heads, return_aux=True)
+    same = (torch.sort(idx, -1).values == torch.sort(aux0["idx"], -1).values).float().mean().item()
+    assert same > 0.85, f"only {same:.2%} of the selected blocks agree with the fp32 selection"
+
+
+def test_module_backward_golden():
+    g = golden("module_bwd")
+    m, sd, heads = _module_pair(g)
+    m.record_idx = True
+    x = g["x"].to(DEV).requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(x, xpos=g["xpos"].to(DEV))
+    y.float().backward(g["dy"].to(DEV))
+    p = {k: v.clone().requires_grad_(True) for k, v in sd.items()}
+    xr = g["x"].clone().requires_grad_(True)
+    y_ref = R.module_forward(p, xr, g["xpos"], heads, idx_override=m.last_idx.cpu())
+    y_ref.backward(g["dy"])
+    assert_bf16_close(y, y_ref, "module y", max_abs=6e-2, mean_abs=8e-3)
+    assert_bf16_close(x.grad, xr.grad, "module dx", max_abs=6e-2, mean_abs=8e-3)
+    for k, prm in m.named_parameters():
+        assert_bf16_close(prm.grad, p[k].grad, "grad " + k, max_abs=6e-2, mean_abs=1e-2)
+
+
+def test_module_under_checkpoint_recompute_is_deterministic():
+    """Pi3_Sparse wraps the block in activation checkpointing when training (pi3_sparse.py:252-253):
+    the recomputed forward must select the same blocks."""
+    import speed3r_b200
+    from torch.utils.checkpoint import checkpoint
+    torch.manual_seed(3)
+    m = speed3r_b200.SparseFlashAttentionRope(256, num_heads=4, qkv_bias=True, qk_norm=True,
+                                              rope=speed3r_b200.RoPE2D()).to(DEV)
+    x = torch.randn(1, 1024, 256, device=DEV, requires_grad=True)
+    ys, xs = torch.meshgrid(torch.arange(32), torch.arange(32), indexing="ij")
+    xpos = torch.stack([ys, xs], -1).view(1, -1, 2).to(DEV)
+    grads = []
+    for use_ckpt in (False, True):
+        x.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = checkpoint(m, x, None, xpos, use_reentrant=False) if use_ckpt else m(x, xpos=xpos)
+        y.float().square().mean().backward()
+        grads.append(x.grad.clone())
+    assert torch.equal(grads[0], grads[1])
+
+
+def test_rejects_cpu_and_fp32():
+    from speed3r_b200 import ops
+    q = torch.randn(1, 1, 32, 64)
+    with pytest.raises(RuntimeError):
+        ops.flash_attn_topk_func(q.bfloat16(), q.bfloat16(), q.bfloat16(), 8)       # CPU tensors
+    with pytest.raises(RuntimeError):
+        ops.flash_attn_topk_func(q.to(DEV), q.to(DEV), q.to(DEV), 8)                # fp32
