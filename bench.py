@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse global-attention layer op at 1000 views (the reference's headline
+setting), on synthetic data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--views V] [--mode fwd|fwdbwd]
+
+One step = one pass of the op over one 1000-view sequence: pool q,k,v (16/16) -> compression
+attention with fused top-32 -> selection attention over the 32 selected 16-token blocks with the
+gated merge fused.  Inputs: q,k,v ~ N(0,1) after a per-head LayerNorm, bf16, [1,16,T,64] with
+T = views*1008; gate = sigmoid(N(0,1)).  The metric is effective sparse TFLOP/s
+(F = 4*Nq*Nc*d*H + 4*T*K*Bs*d*H per step, forward; x3.5 with the backward).
+
+N > 1 (launched with torch.distributed.run): the sequence is partitioned by query blocks over the
+ranks; pooled and token-level K/V are all-gathered (NCCL).  Total work is fixed -> strong scaling.
+
+--impl reference times the CPU restatement of the reference's algorithm (the reference itself is
+Python + Triton and is not present on the benchmark machine) on a bounded sample of the same
+workload, using all host threads.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, D, BS, TOPK, TOK_PER_VIEW = 16, 64, 16, 32, 1008
+
+
+def flops_fwd(T, Nq_rows=None, heads=H):
+    """Effective sparse flops of one forward of the op (optionally for a subset of query blocks)."""
+    nq = T // BS if Nq_rows is None else Nq_rows
+    nc = T // BS
+    f_cmp = 4.0 * nq * nc * D * heads
+    f_sel = 4.0 * (nq * BS) * (TOPK * BS) * D * heads
+    return f_cmp, f_sel
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return dict(hbm_gbs=j["hbm_gbs"], tflops=j["bf16_tflops_sustained"], tflops_burst=j["bf16_tflops"], src="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, tflops_burst=1590.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+                for n, val in zip(names, r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                pass
+        busy = [x for x in sm if mx and x > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the oracle restatement on a bounded sample of the same workload
+# --------------------------------------------------------------------------------------------------
+def cpu_sample(views, seconds_hint=20.0):
+    """One head, the first `nqb` query blocks against ALL pooled keys / token blocks of the head."""
+    import torch
+    from oracle import restatement as R
+    torch.set_num_threads(os.cpu_count() or 1)
+    T = views * TOK_PER_VIEW
+    nc = T // BS
+    nqb = max(8, min(nc, int(2.0e10 / (4.0 * nc * D + 4.0 * BS * TOPK * BS * D))))   # ~20 Gflop of work
+    g = torch.Generator().manual_seed(0)
+    ln = lambda t: torch.nn.functional.layer_norm(t, (D,))
+    q = ln(torch.randn(1, 1, nqb * BS, D, generator=g)).bfloat16().float()
+    k = ln(torch.randn(1, 1, T, D, generator=g)).bfloat16().float()
+    v = ln(torch.randn(1, 1, T, D, generator=g)).bfloat16().float()
+    gate = torch.sigmoid(torch.randn(1, 1, nqb * BS, 2, generator=g))
+
+    def step():
+        q_c, k_c, v_c = R.pool_tokens(q, BS, BS), R.pool_tokens(k, BS, BS), R.pool_tokens(v, BS, BS)
+        o_c, _, idx = R.cmp_attn_topk(q_c, k_c, v_c, TOPK, row_chunk=512)
+        o_s, _ = R.sel_attn(q, k, v, idx, BS, qblock_chunk=256)
+        return R.gated_merge(gate, o_c, o_s, BS)
+
+    f_cmp, f_sel = flops_fwd(T, Nq_rows=nqb, heads=1)
+    sample = (f"1 head, first {nqb} of {nc} query blocks against all {nc} pooled keys and the full K/V of the "
+              f"{views}-view sequence, fp32 torch on {torch.get_num_threads()} threads")
+    return step, f_cmp + f_sel, sample, torch.get_num_threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, fl, sample, cores = cpu_sample(args.views)
+    for _ in range(max(1, min(args.warmup, 1))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = fl / dt / 1e12
+    line = dict(metric="sparse_attn_layer_effective_tflops", value=val, unit="TFLOP/s", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True,
+                scaling="strong", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=workload_config(args),
+                cpu_baseline=dict(value=val, unit="TFLOP/s", cores=cores, kind="port", sample=sample),
+                e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line))
+
+
+def workload_config(args):
+    T = args.views * TOK_PER_VIEW
+    return {"workload": f"sparse global-attention op, {args.mode}, {args.views} views x {TOK_PER_VIEW} tokens "
+                        f"(T={T}), H={H}, d={D}, pool {BS}/{BS}, select block {BS}, top-{TOPK}",
+            "tokens": T, "views": args.views, "mode": args.mode,
+            "parallelism": f"sp{args.gpus}" if args.gpus > 1 else "single",
+            "l2": "inputs (q,k,v: 3 x %.1f GB) larger than the 126 MB L2" % (T * H * D * 2 / 1e9)}
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--views", type=int, default=1000)
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 5:
+            args.steps = 5
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from speed3r_b200 import _lib, ops, seq_parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    args.warmup = max(args.warmup, 3)
+
+    T = args.views * TOK_PER_VIEW
+    t0, t1 = seq_parallel.partition(T, BS, world, rank)
+    Tl = t1 - t0
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    ln = lambda t: torch.nn.functional.layer_norm(t, (D,))
+    q, k, v = (ln(torch.randn(1, H, Tl, D, device=dev, generator=g)).bfloat16() for _ in range(3))
+    gate = torch.sigmoid(torch.randn(1, H, Tl, 2, device=dev, generator=g)).bfloat16()
+    bwd = args.mode == "fwdbwd"
+    if bwd and world > 1:
+        raise SystemExit("fwdbwd is single-GPU in this benchmark")
+    dy = torch.randn(1, Tl, H * D, device=dev, generator=g).bfloat16() if bwd else None
+    side = torch.cuda.Stream() if world > 1 else None
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    marks = []
+
+    def step(record=False):
+        """Returns y; with record=True also appends per-kernel CUDA events (single GPU only)."""
+        if world > 1:
+            y, _ = seq_parallel.sparse_attention_partitioned(
+                q, k, v, gate, BS, TOPK, ops.pool_tokens, lambda a, b, c, kk: ops.flash_attn_topk_func(a, b, c, kk),
+                lambda a, b, c, i, gt, oc, bs: ops.sel_attn_merge_chunked(a, b, c, i, gt, oc, bs), side_stream=side)
+            return y
+        if bwd:
+            ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+        else:
+            ql, kl, vl = q, k, v
+        e = [ev() for _ in range(4)] if record else None
+        if record: e[0].record()
+        qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (ql, kl, vl))
+        if record: e[1].record()
+        o_c, idx = ops.flash_attn_topk_func(qc, kc, vc, TOPK)
+        if record: e[2].record()
+        y = ops.sel_attn_merge(ql, kl, vl, idx, gate, o_c, BS)
+        if record:
+            e[3].record()
+            marks.append(e)
+        if bwd:
+            y.backward(dy)
+        return y
+
+    ctx = torch.enable_grad() if bwd else torch.no_grad()
+    with ctx:
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        torch.cuda.synchronize()
+        s, e_ = ev(), ev()
+        s.record()
+        for _ in range(args.steps):
+            step(record=(world == 1))
+        e_.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        ms = s.elapsed_time(e_) / args.steps
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = tms.item()
+    status = _lib.device_status()
+    if status != 0:
+        raise SystemExit(f"device status word {status}: a kernel gave up a bounded wait")
+
+    f_cmp, f_sel = flops_fwd(T)
+    ftot = (f_cmp + f_sel) * (3.5 if bwd else 1.0)
+    value = ftot / (ms * 1e-3) / 1e12
+    peaks = load_peaks()
+
+    # per-kernel averages (single GPU): pooling, compression attention + top-k, selection + merge
+    roof, kern = None, None
+    if world == 1 and marks:
+        avg = lambda i: sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)
+        t_pool, t_cmp, t_sel = avg(0), avg(1), avg(2)
+        pool_bytes = 3 * T * H * D * 2 + 3 * (T // BS) * H * D * 2
+        sel_bytes = (T // BS) * H * TOPK * BS * D * 4 + 2 * T * H * D * 2 + T * H * 2 * 2
+        kern = {"pool_ms": t_pool, "cmp_attn_topk_ms": t_cmp, "sel_attn_merge_ms": t_sel,
+                "pool_gbs": pool_bytes / t_pool / 1e6, "pool_frac_hbm": pool_bytes / t_pool / 1e6 / peaks["hbm_gbs"],
+                "cmp_tflops": f_cmp / t_cmp / 1e9, "sel_gather_gbs": sel_bytes / t_sel / 1e6,
+                "sel_frac_hbm": sel_bytes / t_sel / 1e6 / peaks["hbm_gbs"], "sel_tflops": f_sel / t_sel / 1e9}
+        ach = f_cmp / t_cmp / 1e9
+        roof = {"kernel": "cmp_fwd_kernel (compression attention + top-k)", "bound": "tensor", "achieved": ach,
+                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": None,
+                "peak_source": f"{peaks['src']} sustained bf16 (kernel timed inside a long step)"}
+
+    # end to end through the public op functions with HOST buffers (pinned), copies inside the timing
+    e2e = None
+    if world == 1 and not args.no_e2e and not bwd:
+        hq, hk, hv, hg = (t.cpu().pin_memory() for t in (q, k, v, gate))
+        hy = torch.empty(1, Tl, H * D, dtype=torch.bfloat16).pin_memory()
+        dq_, dk_, dv_, dg_ = (torch.empty_like(t) for t in (q, k, v, gate))
+
+        def e2e_step():
+            dq_.copy_(hq, non_blocking=True); dk_.copy_(hk, non_blocking=True)
+            dv_.copy_(hv, non_blocking=True); dg_.copy_(hg, non_blocking=True)
+            qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (dq_, dk_, dv_))
+            o_c, idx = ops.flash_attn_topk_func(qc, kc, vc, TOPK)
+            y = ops.sel_attn_merge(dq_, dk_, dv_, idx, dg_, o_c, BS)
+            hy.copy_(y, non_blocking=True)
+
+        with torch.no_grad():
+            e2e_step()
+            torch.cuda.synchronize()
+            n = max(2, min(args.steps, 5))
+            s2, e2 = ev(), ev()
+            s2.record()
+            for _ in range(n):
+                e2e_step()
+            e2.record()
+            torch.cuda.synchronize()
+        ems = s2.elapsed_time(e2) / n
+        e2e = {"value": (f_cmp + f_sel) / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ems,
+               "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)),
+               "d2h_bytes_per_step": hy.numel() * hy.element_size()}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cstep, cfl, sample, cores = cpu_sample(args.views)
+        cstep()
+        c0 = time.perf_counter()
+        nrep = 2
+        for _ in range(nrep):
+            cstep()
+        cdt = (time.perf_counter() - c0) / nrep
+        cpu = {"value": cfl / cdt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+               "s_per_sample": cdt}
+
+    if rank == 0:
+        line = dict(metric="sparse_attn_layer_effective_tflops", value=value, unit="TFLOP/s", n_gpus=world,
+                    steps=args.steps, warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong",
+                    vs_baseline=None, dtype="bf16", data="synthetic", config=workload_config(args),
+                    views_per_s=args.views / (ms * 1e-3), clocks=clocks, e2e=e2e,
+                    gpu_launches=args.steps * (5 if not bwd else 5 + 3 + 1 + 6 + 2 + 3),
+                    roofline=roof, kernels=kern, cpu_baseline=cpu)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

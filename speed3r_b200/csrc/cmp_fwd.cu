@@ -10,35 +10,35 @@
 //   warps 4-7, 8-11   two softmax warpgroups, one per 128-row query tile; thread = row
 // A CTA owns 256 query rows (two tiles sharing every K/V tile).  Tensor memory: S_A, S_B (128
 // fp32 columns each), O_A, O_B (64 each).  P (bf16) is written back over the S columns and fed to
-// the second MMA straight from tensor memory, or goes through shared memory (kPTmem = false).
+// the second MMA straight from tensor memory.
 //
 // Online softmax with a lazily updated maximum: the exponent offset only moves when the running
 // maximum grows by more than 2^8, and only then is O rescaled in tensor memory, by the softmax
 // threads themselves (each owns one TMEM lane).
 //
-// Top-k: every warp keeps, for each of its 32 rows, the row's current best `topk` entries in
-// shared memory, one entry per lane, as  key(score) << 32 | ~column  (larger = better; ties on the
-// score go to the smaller column).  A lane tests 16-column chunks against its row's threshold
-// (the smallest kept score); a hit is inserted by the whole warp: redux.min finds the entry to
-// evict.  Entries start at zero, which decodes to column Nc-1, the reference's padding.
+// Top-k.  Per row, shared memory holds the best 32 entries (key(score), column) SORTED across the
+// lanes of the row's warp (slot l belongs to lane l), plus a small pending buffer.  A thread tests
+// 16-column chunks of its row against the row's threshold (the topk-th kept score) and appends
+// hits to the pending buffer on its own (no warp cooperation); when a buffer is full the warp
+// merges it into the sorted list in one pass (merge ranks from one ballot per pending entry) and
+// the threshold rises.  Ties on the score keep the smaller column first because columns arrive in
+// ascending order.  Slots start empty (key 0), which decodes to column Nc-1, the reference's padding.
 #include "common.cuh"
 
 namespace s3r {
 
 constexpr int kCmpThreads = 384;
 constexpr int kTileBytes = 128 * 128;        // 128 rows x 64 bf16
-constexpr int kListBytes = 256 * 32 * 8;     // 256 rows x 32 entries x u64
-
-template <bool kPTmem>
-struct CmpCfg {
-  static constexpr int kStages = kPTmem ? 3 : 2;
-  static constexpr int kOffQ = 0;
-  static constexpr int kOffK = 2 * kTileBytes;
-  static constexpr int kOffV = kOffK + kStages * kTileBytes;
-  static constexpr int kOffP = kOffV + kStages * kTileBytes;
-  static constexpr int kOffL = kOffP + (kPTmem ? 0 : 4 * kTileBytes);
-  static constexpr int kSmemBytes = kOffL + kListBytes + 1024;
-};
+constexpr int kListBytes = 256 * 32 * 8;     // 256 rows x 32 sorted entries x (key, column)
+constexpr int kPend = 8;                     // pending entries per row
+constexpr int kPendBytes = 256 * kPend * 8;
+constexpr int kStages = 3;
+constexpr int kOffQ = 0;
+constexpr int kOffK = 2 * kTileBytes;
+constexpr int kOffV = kOffK + kStages * kTileBytes;
+constexpr int kOffL = kOffV + kStages * kTileBytes;
+constexpr int kOffPend = kOffL + kListBytes;
+constexpr int kCmpSmemBytes = kOffPend + kPendBytes + 1024;
 
 struct CmpCtl {
   uint64_t q_full, o_full;
@@ -52,7 +52,7 @@ struct CmpParams {
   __nv_bfloat16* o;
   float* lse;
   int32_t* idx;
-  int Nq, Nc, topk;
+  int Nq, Nc, topk, flags;
   float c_scale;        // softmax scale * log2(e)
   uint32_t* status;
 };
@@ -63,50 +63,58 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
   return __uint_as_float(b);
 }
 
-// Warp-cooperative insertion of (score, column) into the list of row `src` of this warp.
-// Returns the sortable key of the smallest kept score afterwards (0 while the list has free slots).
-__device__ __forceinline__ uint32_t topk_insert(uint64_t* list_row, int lane, int topk, float score, int column) {
-  const uint32_t key = sortable_key(score);
-  uint64_t ent = (lane < topk) ? list_row[lane] : ~0ull;
-  uint32_t hi = static_cast<uint32_t>(ent >> 32);
-  const uint32_t lo = static_cast<uint32_t>(ent);
-  uint32_t mn_hi = redux_min_u32(hi);
-  if (key > mn_hi) {
-    const uint32_t mn_lo = redux_min_u32(hi == mn_hi ? lo : 0xffffffffu);
-    const uint32_t match = __ballot_sync(0xffffffffu, hi == mn_hi && lo == mn_lo);
-    if (lane == __ffs(match) - 1) {
-      list_row[lane] = (static_cast<uint64_t>(key) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(column));
-      hi = key;
-    }
-    mn_hi = redux_min_u32(hi);
-    __syncwarp();
-  }
-  return mn_hi;
-}
-
-// Scan 16 consecutive logits of this thread's row (x[0..15], first column col0) for top-k hits.
-__device__ __forceinline__ void topk_scan16(const uint32_t* x, int col0, int nvalid, bool hot, float& thr,
-                                            uint64_t* warp_lists, int lane, int topk) {
+// Thread-local: append this thread's hits among x[e_start..15] (first column col0) to its row's
+// pending buffer.  Stops at the first hit that does not fit and leaves e_start there; e_start = 16
+// when the chunk is finished.
+__device__ __forceinline__ void topk_append16(const uint32_t* x, int col0, int nvalid, float thr, uint2* my_pend,
+                                              int& cnt, int& e_start) {
+  bool full = false;
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     const float v = __uint_as_float(x[e]);
-    const bool cand = hot && (e < nvalid) && (v >= thr);
-    uint32_t mask = __ballot_sync(0xffffffffu, cand);
-    while (mask) {
-      const int src = __ffs(mask) - 1;
-      mask &= mask - 1;
-      const float sv = __shfl_sync(0xffffffffu, v, src);
-      const uint32_t mn = topk_insert(warp_lists + src * 32, lane, topk, sv, col0 + e);
-      if (lane == src) thr = key_to_float(mn);
+    if (!full && e >= e_start && e < nvalid && v >= thr) {
+      if (cnt < kPend) {
+        my_pend[cnt] = make_uint2(sortable_key(v), static_cast<uint32_t>(col0 + e));
+        ++cnt;
+      } else {
+        full = true;
+        e_start = e;
+      }
     }
   }
+  if (!full) e_start = 16;
 }
 
-template <bool kPTmem>
+// Warp-cooperative merge of the m pending entries of one row into its sorted list.  Old entry l
+// moves to l + (#pending better than it); pending j lands at (#old >= it) + (#pending better than
+// it).  An old entry wins a tie on the key (its column is smaller); pending entries tie-break on
+// the column.  Returns the key in slot topk-1 afterwards (0 while fewer than topk real entries).
+__device__ __forceinline__ uint32_t topk_flush_row(uint2* list_row, const uint2* pend_row, int m, int lane, int topk) {
+  __syncwarp();
+  const uint2 old = list_row[lane];
+  const uint2 mine = (lane < m) ? pend_row[lane] : make_uint2(0u, 0u);
+  int shift = 0, myrank = 0;
+#pragma unroll
+  for (int j = 0; j < kPend; ++j) {
+    if (j < m) {                                     // warp-uniform
+      const uint2 pj = pend_row[j];
+      const bool pb = pj.x > old.x;
+      shift += pb ? 1 : 0;
+      const int nge = __popc(__ballot_sync(0xffffffffu, !pb));
+      const bool jb = (pj.x > mine.x) || (pj.x == mine.x && pj.y < mine.y);
+      myrank += (jb ? 1 : 0) + (lane == j ? nge : 0);
+    }
+  }
+  __syncwarp();
+  if (lane + shift < 32) list_row[lane + shift] = old;
+  if (lane < m && myrank < 32) list_row[myrank] = mine;
+  __syncwarp();
+  return list_row[topk - 1].x;
+}
+
 __global__ void __launch_bounds__(kCmpThreads, 1)
 cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const CmpParams p) {
-  using C = CmpCfg<kPTmem>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ CmpCtl ctl;
 
@@ -118,7 +126,8 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
-  uint64_t* lists = reinterpret_cast<uint64_t*>(sptr + C::kOffL);
+  uint2* lists = reinterpret_cast<uint2*>(sptr + kOffL);
+  uint2* pends = reinterpret_cast<uint2*>(sptr + kOffPend);
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -140,7 +149,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     tmem_alloc(&ctl.tmem_base, 512);
     tmem_relinquish();
   }
-  for (int i = threadIdx.x; i < 256 * 32; i += kCmpThreads) lists[i] = 0ull;
+  for (int i = threadIdx.x; i < 256 * 32; i += kCmpThreads) lists[i] = make_uint2(0u, 0u);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -151,25 +160,25 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&ctl.q_full, 2 * kTileBytes);
-      tma_load_3d(sbase + C::kOffQ, &map_q, &ctl.q_full, 0, q0, bh);
-      tma_load_3d(sbase + C::kOffQ + kTileBytes, &map_q, &ctl.q_full, 0, q0 + 128, bh);
+      tma_load_3d(sbase + kOffQ, &map_q, &ctl.q_full, 0, q0, bh);
+      tma_load_3d(sbase + kOffQ + kTileBytes, &map_q, &ctl.q_full, 0, q0 + 128, bh);
       int issued = 0;
       for (int j = 0; j < ntiles; ++j) {
-        const int s = j % C::kStages;
-        const uint32_t ph = (j / C::kStages) & 1;
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
         if (!mbar_wait(&ctl.k_empty[s], ph ^ 1, abort_flag)) break;
         mbar_expect_tx(&ctl.k_full[s], kTileBytes);
-        tma_load_3d(sbase + C::kOffK + s * kTileBytes, &map_k, &ctl.k_full[s], 0, j * 128, bh);
+        tma_load_3d(sbase + kOffK + s * kTileBytes, &map_k, &ctl.k_full[s], 0, j * 128, bh);
         if (!mbar_wait(&ctl.v_empty[s], ph ^ 1, abort_flag)) { issued = j + 1; break; }   // K of tile j is in flight
         mbar_expect_tx(&ctl.v_full[s], kTileBytes);
-        tma_load_3d(sbase + C::kOffV + s * kTileBytes, &map_v, &ctl.v_full[s], 0, j * 128, bh);
+        tma_load_3d(sbase + kOffV + s * kTileBytes, &map_v, &ctl.v_full[s], 0, j * 128, bh);
         issued = j + 1;
       }
       if (*abort_flag) {
         // give copies already in flight a bounded chance to land before the CTA's memory is released
-        for (int j = max(0, issued - C::kStages); j < issued; ++j) {
+        for (int j = max(0, issued - kStages); j < issued; ++j) {
           volatile uint32_t dummy = 0;
-          mbar_wait(&ctl.k_full[j % C::kStages], (j / C::kStages) & 1, &dummy);
+          mbar_wait(&ctl.k_full[j % kStages], (j / kStages) & 1, &dummy);
         }
       }
     }
@@ -177,25 +186,18 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 0, 1);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 0, 1);   // V tile is [keys][d]: N contiguous
       auto issue_qk = [&](int t, int s) {
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + t * 128, umma_desc_sw128(sbase + C::kOffQ + t * kTileBytes + ks * 32),
-                  umma_desc_sw128(sbase + C::kOffK + s * kTileBytes + ks * 32), idesc_qk, ks > 0);
+          umma_ss(tmem + t * 128, umma_desc_sw128(sbase + kOffQ + t * kTileBytes + ks * 32),
+                  umma_desc_sw128(sbase + kOffK + s * kTileBytes + ks * 32), idesc_qk, ks > 0);
       };
       auto issue_pv = [&](int t, int s, bool acc) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bdesc = umma_desc_sw128(sbase + C::kOffV + s * kTileBytes + ks * 2048);
-          if constexpr (kPTmem) {
-            umma_ts(tmem + 256 + t * 64, tmem + t * 128 + ks * 8, bdesc, idesc_pv, (acc || ks > 0) ? 1u : 0u);
-          } else {
-            umma_ss(tmem + 256 + t * 64,
-                    umma_desc_sw128(sbase + C::kOffP + t * 2 * kTileBytes + (ks >> 2) * kTileBytes + (ks & 3) * 32), bdesc,
-                    idesc_pv, (acc || ks > 0) ? 1u : 0u);
-          }
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + 256 + t * 64, tmem + t * 128 + ks * 8, umma_desc_sw128(sbase + kOffV + s * kTileBytes + ks * 2048),
+                  idesc_pv, (acc || ks > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(&ctl.q_full, 0, abort_flag) && mbar_wait(&ctl.k_full[0], 0, abort_flag);
       if (ok) {
@@ -206,11 +208,11 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         umma_commit(&ctl.s_full[1]);
         umma_commit(&ctl.k_empty[0]);
         for (int j = 0; j < ntiles && ok; ++j) {
-          const int s = j % C::kStages;
+          const int s = j % kStages;
           const bool nxt = j + 1 < ntiles;
-          const int sn = (j + 1) % C::kStages;
-          ok = mbar_wait(&ctl.v_full[s], (j / C::kStages) & 1, abort_flag);
-          if (ok && nxt) ok = mbar_wait(&ctl.k_full[sn], ((j + 1) / C::kStages) & 1, abort_flag);
+          const int sn = (j + 1) % kStages;
+          ok = mbar_wait(&ctl.v_full[s], (j / kStages) & 1, abort_flag);
+          if (ok && nxt) ok = mbar_wait(&ctl.k_full[sn], ((j + 1) / kStages) & 1, abort_flag);
           for (int t = 0; t < 2 && ok; ++t) {
             ok = mbar_wait(&ctl.p_full[t], j & 1, abort_flag);
             if (!ok) break;
@@ -237,12 +239,29 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int quarter = warp & 3;
     const int row_local = t * 128 + quarter * 32 + lane;      // 0..255 inside the CTA
     const int grow = q0 + row_local;
-    uint64_t* warp_lists = lists + (t * 128 + quarter * 32) * 32;
+    uint2* warp_lists = lists + (t * 128 + quarter * 32) * 32;
+    uint2* warp_pend = pends + (t * 128 + quarter * 32) * kPend;
+    uint2* my_pend = warp_pend + lane * kPend;
     const uint32_t t_s = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + t * 128;
     const uint32_t t_o = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + 256 + t * 64;
     const float cs = p.c_scale;
     float m_used = -INFINITY, l = 0.f, thr = -INFINITY;
+    int cnt = 0;
     bool ok = true;
+
+    // merge the pending buffers of the rows in `mask` into their sorted lists
+    auto flush_rows = [&](uint32_t mask) {
+      while (mask) {
+        const int src = __ffs(mask) - 1;
+        mask &= mask - 1;
+        const int m = __shfl_sync(0xffffffffu, cnt, src);
+        const uint32_t kth = topk_flush_row(warp_lists + src * 32, warp_pend + src * kPend, m, lane, p.topk);
+        if (lane == src) {
+          cnt = 0;
+          thr = key_to_float(kth);
+        }
+      }
+    };
 
     for (int j = 0; j < ntiles; ++j) {
       if (!mbar_wait_warp(&ctl.s_full[t], j & 1, abort_flag)) { ok = false; break; }
@@ -271,8 +290,15 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int i = 1; i < 16; ++i) cm = fmaxf(cm, __uint_as_float(x[hf * 16 + i]));
           rmax = fmaxf(rmax, cm);
           const bool hot = (cm >= thr);
-          if (__any_sync(0xffffffffu, hot))
-            topk_scan16(x + hf * 16, col0 + c4 * 32 + hf * 16, nvalid - hf * 16, hot, thr, warp_lists, lane, p.topk);
+          if (!(p.flags & 2) && __any_sync(0xffffffffu, hot)) {
+            int e_start = hot ? 0 : 16;
+            while (true) {
+              topk_append16(x + hf * 16, col0 + c4 * 32 + hf * 16, nvalid - hf * 16, thr, my_pend, cnt, e_start);
+              const uint32_t fullmask = __ballot_sync(0xffffffffu, e_start < 16);
+              if (!fullmask) break;
+              flush_rows(fullmask);
+            }
+          }
         }
       }
 
@@ -301,7 +327,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_st_wait();
       }
 
-      // pass 2: P = exp2(s*c - m), row sum, bf16 P to tensor memory (or shared memory)
+      // pass 2: P = exp2(s*c - m), row sum, bf16 P back over the S columns
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -322,23 +348,10 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ls[i & 3] += p0 + p1;
           pk[i] = pack_bf16(p0, p1);
         }
-        if constexpr (kPTmem) {
-          tmem_st16(t_s + c4 * 16, pk);
-        } else {
-          uint8_t* pbase = sptr + C::kOffP + t * 2 * kTileBytes + (c4 >> 1) * kTileBytes;
-          const uint32_t r = quarter * 32 + lane;
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(pbase + swz128(r, (c4 & 1) * 4 + i)) =
-                make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-        }
+        tmem_st16(t_s + c4 * 16, pk);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      if constexpr (kPTmem) {
-        tmem_st_wait();
-      } else {
-        fence_proxy_async_smem();
-      }
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&ctl.p_full[t]);
     }
@@ -364,18 +377,15 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                                 pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
         }
       }
+      flush_rows(__ballot_sync(0xffffffffu, cnt > 0));
       __syncwarp();
       const int wrow0 = q0 + t * 128 + quarter * 32;
+      // the lists are sorted: slot l is rank l; an empty slot decodes to column Nc-1
       for (int r = 0; r < 32 && wrow0 + r < p.Nq; ++r) {
-        const uint64_t ent = (lane < p.topk) ? warp_lists[r * 32 + lane] : 0ull;
-        int rank = 0;
-        for (int i = 0; i < p.topk; ++i) {
-          const uint64_t other = __shfl_sync(0xffffffffu, ent, i);
-          rank += (other > ent) || (other == ent && i < lane);
-        }
+        const uint2 ent = warp_lists[r * 32 + lane];
         if (lane < p.topk)
-          p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * p.topk + rank] =
-              (ent == 0ull) ? (p.Nc - 1) : static_cast<int32_t>(~static_cast<uint32_t>(ent));
+          p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * p.topk + lane] =
+              (ent.x == 0u) ? (p.Nc - 1) : static_cast<int32_t>(ent.y);
       }
     }
     if (!ok && lane == 0) atomicOr(p.status, kStatusWaitTimeout);
@@ -386,29 +396,11 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (warp == 2) tmem_dealloc(tmem, 512);
 }
 
-template <bool kPTmem>
-static int launch_cmp_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CmpParams& p,
-                          int BH, cudaStream_t st) {
-  using C = CmpCfg<kPTmem>;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  S3R_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel<kPTmem>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    attr_set[dev] = true;
-  }
-  const int64_t grid = static_cast<int64_t>(BH) * ((p.Nq + 255) / 256);
-  S3R_REQUIRE(grid < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_cmp_attn_topk_fwd: grid too large");
-  cmp_fwd_kernel<kPTmem><<<static_cast<unsigned>(grid), kCmpThreads, C::kSmemBytes, st>>>(mq, mk, mv, p);
-  S3R_CUDA(cudaGetLastError());
-  return 0;
-}
-
 }  // namespace s3r
 
 using namespace s3r;
 
-// Debug switch for bring-up: 0 = P through tensor memory (default), 1 = P through shared memory.
+// Profiling switch: bit 1 set = skip the top-k scan (idx is then meaningless).  0 by default.
 static int g_cmp_variant = 0;
 extern "C" void s3r_debug_set_cmp_variant(int v) { g_cmp_variant = v; }
 
@@ -445,11 +437,21 @@ extern "C" int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const voi
   p.o = static_cast<__nv_bfloat16*>(o_c);
   p.lse = lse;
   p.idx = idx;
-  p.Nq = Nq; p.Nc = Nc; p.topk = topk;
+  p.Nq = Nq; p.Nc = Nc; p.topk = topk; p.flags = g_cmp_variant;
   p.c_scale = scale * 1.4426950408889634f;
   p.status = device_status_ptr();
   S3R_REQUIRE(p.status != nullptr, S3R_ERR_DRIVER, "s3r_cmp_attn_topk_fwd: could not resolve the device status word");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (g_cmp_variant == 1) return launch_cmp_fwd<false>(mq, mk, mv, p, BH, st);
-  return launch_cmp_fwd<true>(mq, mk, mv, p, BH, st);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  S3R_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmpSmemBytes));
+    attr_set[dev] = true;
+  }
+  const int64_t grid = static_cast<int64_t>(BH) * ((Nq + 255) / 256);
+  S3R_REQUIRE(grid < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_cmp_attn_topk_fwd: grid too large");
+  cmp_fwd_kernel<<<static_cast<unsigned>(grid), kCmpThreads, kCmpSmemBytes, st>>>(mq, mk, mv, p);
+  S3R_CUDA(cudaGetLastError());
+  return 0;
 }

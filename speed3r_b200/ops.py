@@ -381,6 +381,19 @@ def sel_attn_merge(q, k, v, topk_idx, gate, o_c, block_size, softmax_scale=None)
     return _SelMerge.apply(q, k, v, topk_idx, gate, o_c, int(block_size), float(softmax_scale))
 
 
+def sel_attn_merge_chunked(q, k_chunks, v_chunks, topk_idx, gate, o_c, block_size, softmax_scale=None):
+    """Forward-only form of ``sel_attn_merge`` for sequence-partitioned inference: the keys and
+    values are the all-gathered ``[G,B,H,Tk/G,d]`` chunks (rank order = sequence order), read in
+    place; ``q``, ``gate``, ``o_c`` and ``topk_idx`` are the local query rows; ``topk_idx`` holds
+    GLOBAL key-block numbers."""
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    with torch.no_grad():
+        _, _, y = _sel_fwd(q, k_chunks, v_chunks, topk_idx, gate, o_c, int(block_size), float(softmax_scale),
+                           False, False, int(k_chunks.shape[0]))
+    return y
+
+
 # ------------------------------------------------------------------------------------------------
 # device-side cross-checks (tests only)
 # ------------------------------------------------------------------------------------------------

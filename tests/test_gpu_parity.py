@@ -76,7 +76,7 @@ def _cmp_case(q, k, v, topk, exact=False, variant=0, what=""):
     assert_bf16_close(lse, lse_ref, what + " lse", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0])
 @pytest.mark.parametrize("name", ["cmp_basic", "cmp_ragged", "cmp_rect", "cmp_short", "cmp_ties"])
 def test_cmp_attn_topk_golden(name, variant):
     g = golden(name)
@@ -84,9 +84,9 @@ def test_cmp_attn_topk_golden(name, variant):
               what=f"{name}/v{variant}")
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0])
 @pytest.mark.parametrize("B,H,Nq,Nc,topk", [(1, 4, 1000, 1000, 32), (2, 2, 300, 2500, 16), (1, 2, 257, 129, 32),
-                                            (1, 1, 4032, 4032, 32), (1, 2, 5, 40, 8)])
+                                            (1, 1, 4032, 4032, 32), (1, 2, 5, 40, 8), (1, 2, 700, 900, 1)])
 def test_cmp_attn_topk_seeded(B, H, Nq, Nc, topk, variant):
     q, k, v = randn(11, B, H, Nq, 64), randn(12, B, H, Nc, 64), randn(13, B, H, Nc, 64)
     _cmp_case(q, k, v, topk, variant=variant, what=f"seeded {Nq}x{Nc}/v{variant}")
