@@ -3,47 +3,53 @@
 // selection branch will read).
 //
 // Bound: tensor cores in principle (4*Nq*Nc*64 flop per head), with the softmax exponentials and
-// the top-k threshold tests as the practical co-limit, so the MMAs are taken off the issue path:
-//   warp 0  (1 lane)  TMA producer: Q tile pair once, then K and V tiles of 128 keys into rings
-//   warp 1  (1 lane)  tcgen05.mma issuer: S = Q K^T (M=128,N=128) and O += P V (M=128,N=64)
-//   warp 2            tensor-memory allocator
-//   warps 4-7, 8-11   two softmax warpgroups, one per 128-row query tile; thread = row
-// A CTA owns 256 query rows (two tiles sharing every K/V tile).  Tensor memory: S_A, S_B (128
-// fp32 columns each), O_A, O_B (64 each).  P (bf16) is written back over the S columns and fed to
-// the second MMA straight from tensor memory.
+// the top-k threshold tests as the practical co-limit.  The MMAs are taken off the issue path and
+// the two per-element jobs run on different warps so that their latencies overlap:
+//   warp 0  (1 lane)   TMA producer: Q tile pair once, then K and V tiles of 128 keys into rings
+//   warp 1  (1 lane)   tcgen05.mma issuer: S = Q K^T (M=128,N=128) and O += P V (M=128,N=64)
+//   warp 2             tensor-memory allocator
+//   warps 4-7, 8-11    softmax warpgroups, one per 128-row query tile; thread = row
+//   warps 12-15, 16-19 top-k warpgroups, one per query tile; thread = row, reading the same S
+// A CTA owns 256 query rows (two tiles sharing every K/V tile).  Tensor memory (512 columns):
+// S_A, S_B (128 fp32 columns each), O_A, O_B (64 each), P_A, P_B (bf16 pairs, 64 each).  P is fed
+// to the second MMA straight from tensor memory.  S of a tile may be overwritten by the next
+// Q K^T only after both its softmax and its top-k warpgroup have read it.
 //
 // Online softmax with a lazily updated maximum: the exponent offset only moves when the running
 // maximum grows by more than 2^8, and only then is O rescaled in tensor memory, by the softmax
 // threads themselves (each owns one TMEM lane).
 //
-// Top-k.  Per row, shared memory holds the best 32 entries (key(score), column) SORTED across the
-// lanes of the row's warp (slot l belongs to lane l), plus a small pending buffer.  A thread tests
-// 16-column chunks of its row against the row's threshold (the topk-th kept score) and appends
-// hits to the pending buffer on its own (no warp cooperation); when a buffer is full the warp
-// merges it into the sorted list in one pass (merge ranks from one ballot per pending entry) and
-// the threshold rises.  Ties on the score keep the smaller column first because columns arrive in
-// ascending order.  Slots start empty (key 0), which decodes to column Nc-1, the reference's padding.
+// Top-k.  Per row, shared memory holds the best 32 entries (key(score), column), sorted, slot 0
+// best.  The row's threshold is the topk-th kept score.
+//   * first kEarlyTiles tiles (hits are dense): every thread inserts its own hits into its own
+//     row by shifting, all lanes in parallel;
+//   * afterwards (hits are rare): a thread finds hot groups of 4 columns from the maxima of its
+//     max tree; a hit is inserted by the whole warp with one ballot and one shuffle-up (lane l
+//     owns slot l of the row being updated).
+// Ties on the score keep the smaller column first because columns arrive in ascending order.
+// Slots start empty (key 0), which decodes to column Nc-1, the reference's padding.
 #include "common.cuh"
 
 namespace s3r {
 
-constexpr int kCmpThreads = 384;
+constexpr int kCmpThreads = 640;
 constexpr int kTileBytes = 128 * 128;        // 128 rows x 64 bf16
-constexpr int kListBytes = 256 * 32 * 8;     // 256 rows x 32 sorted entries x (key, column)
-constexpr int kPend = 8;                     // pending entries per row
-constexpr int kPendBytes = 256 * kPend * 8;
+constexpr int kListStride = 33;              // entries per row: 32 + 1 of padding (bank spread)
+constexpr int kListBytes = 256 * kListStride * 8;
 constexpr int kStages = 3;
+constexpr int kEarlyTiles = 8;
 constexpr int kOffQ = 0;
 constexpr int kOffK = 2 * kTileBytes;
 constexpr int kOffV = kOffK + kStages * kTileBytes;
 constexpr int kOffL = kOffV + kStages * kTileBytes;
-constexpr int kOffPend = kOffL + kListBytes;
-constexpr int kCmpSmemBytes = kOffPend + kPendBytes + 1024;
+constexpr int kCmpSmemBytes = kOffL + kListBytes + 1024;
+// tensor-memory columns
+constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 
 struct CmpCtl {
   uint64_t q_full, o_full;
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-  uint64_t s_full[2], p_full[2];
+  uint64_t s_full[2], p_full[2], tk_done[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -57,59 +63,66 @@ struct CmpParams {
   uint32_t* status;
 };
 
+// Threshold for the float pre-filter `score > thr`: a score can only enter a full list if its key
+// is strictly greater than the key in slot topk-1 (an equal key loses to the older, smaller
+// column), so rows full of equal scores stop producing hits once their list is full.  The one
+// place where float order and key order disagree is -0.0 < +0.0: a kept -0.0 yields a threshold
+// just below zero so that +0.0 still passes the pre-filter (the exact test is on the keys).
 __device__ __forceinline__ float key_to_float(uint32_t key) {
-  if (key == 0u) return -INFINITY;            // empty slot: everything qualifies
+  if (key == 0u) return -INFINITY;            // empty slot: every finite score qualifies
+  if (key == 0x7fffffffu) return __uint_as_float(0x80000001u);   // -0.0 -> largest negative subnormal
   const uint32_t b = (key & 0x80000000u) ? (key ^ 0x80000000u) : ~key;
   return __uint_as_float(b);
 }
 
-// Thread-local: append this thread's hits among x[e_start..15] (first column col0) to its row's
-// pending buffer.  Stops at the first hit that does not fit and leaves e_start there; e_start = 16
-// when the chunk is finished.
-__device__ __forceinline__ void topk_append16(const uint32_t* x, int col0, int nvalid, float thr, uint2* my_pend,
-                                              int& cnt, int& e_start) {
-  bool full = false;
-#pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    const float v = __uint_as_float(x[e]);
-    if (!full && e >= e_start && e < nvalid && v >= thr) {
-      if (cnt < kPend) {
-        my_pend[cnt] = make_uint2(sortable_key(v), static_cast<uint32_t>(col0 + e));
-        ++cnt;
-      } else {
-        full = true;
-        e_start = e;
-      }
-    }
+// Thread-local insertion into this thread's own row (sorted, 32 slots): shift worse entries down.
+__device__ __noinline__ void topk_insert_own(uint2* row, uint32_t key, uint32_t column) {
+  if (key <= row[31].x) return;                // an equal key loses to the older, smaller column
+  int s = 31;
+  while (s > 0) {
+    const uint2 prev = row[s - 1];
+    if (prev.x >= key) break;
+    row[s] = prev;
+    --s;
   }
-  if (!full) e_start = 16;
+  row[s] = make_uint2(key, column);
 }
 
-// Warp-cooperative merge of the m pending entries of one row into its sorted list.  Old entry l
-// moves to l + (#pending better than it); pending j lands at (#old >= it) + (#pending better than
-// it).  An old entry wins a tie on the key (its column is smaller); pending entries tie-break on
-// the column.  Returns the key in slot topk-1 afterwards (0 while fewer than topk real entries).
-__device__ __forceinline__ uint32_t topk_flush_row(uint2* list_row, const uint2* pend_row, int m, int lane, int topk) {
-  __syncwarp();
-  const uint2 old = list_row[lane];
-  const uint2 mine = (lane < m) ? pend_row[lane] : make_uint2(0u, 0u);
-  int shift = 0, myrank = 0;
-#pragma unroll
-  for (int j = 0; j < kPend; ++j) {
-    if (j < m) {                                     // warp-uniform
-      const uint2 pj = pend_row[j];
-      const bool pb = pj.x > old.x;
-      shift += pb ? 1 : 0;
-      const int nge = __popc(__ballot_sync(0xffffffffu, !pb));
-      const bool jb = (pj.x > mine.x) || (pj.x == mine.x && pj.y < mine.y);
-      myrank += (jb ? 1 : 0) + (lane == j ? nge : 0);
+// Warp-cooperative insertion into the row `list_row` (lane l owns slot l).  The insert position is
+// the number of kept keys >= the new key; lanes at and below it shift down by one.
+// Returns the key in slot topk-1 afterwards (0 while fewer than topk real entries exist).
+__device__ __forceinline__ uint32_t topk_insert_coop(uint2* list_row, int lane, int topk, float score, int column) {
+  const uint32_t key = sortable_key(score);
+  uint2 ent = list_row[lane];
+  const int pos = __popc(__ballot_sync(0xffffffffu, ent.x >= key));
+  if (pos < topk) {                                   // warp-uniform
+    const uint32_t up_k = __shfl_up_sync(0xffffffffu, ent.x, 1);
+    const uint32_t up_c = __shfl_up_sync(0xffffffffu, ent.y, 1);
+    if (lane >= pos) {
+      ent.x = (lane == pos) ? key : up_k;
+      ent.y = (lane == pos) ? static_cast<uint32_t>(column) : up_c;
+      list_row[lane] = ent;
     }
   }
-  __syncwarp();
-  if (lane + shift < 32) list_row[lane + shift] = old;
-  if (lane < m && myrank < 32) list_row[myrank] = mine;
-  __syncwarp();
-  return list_row[topk - 1].x;
+  return __shfl_sync(0xffffffffu, ent.x, topk - 1);
+}
+
+// Four consecutive logits of this thread's row: ballot the hits and insert them one by one.
+__device__ __forceinline__ void topk_scan4(const uint32_t* x, int col0, int nvalid, bool hot, float& thr,
+                                           uint2* warp_lists, int lane, int topk) {
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float v = __uint_as_float(x[e]);
+    const bool cand = hot && (e < nvalid) && (v > thr);
+    uint32_t mask = __ballot_sync(0xffffffffu, cand);
+    while (mask) {
+      const int src = __ffs(mask) - 1;
+      mask &= mask - 1;
+      const float sv = __shfl_sync(0xffffffffu, v, src);
+      const uint32_t kth = topk_insert_coop(warp_lists + src * kListStride, lane, topk, sv, col0 + e);
+      if (lane == src) thr = key_to_float(kth);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kCmpThreads, 1)
@@ -127,7 +140,6 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
   uint2* lists = reinterpret_cast<uint2*>(sptr + kOffL);
-  uint2* pends = reinterpret_cast<uint2*>(sptr + kOffPend);
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -142,6 +154,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int t = 0; t < 2; ++t) {
       mbar_init(&ctl.s_full[t], 1);
       mbar_init(&ctl.p_full[t], 128);
+      mbar_init(&ctl.tk_done[t], 128);
     }
     mbar_fence_init();
   }
@@ -149,7 +162,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     tmem_alloc(&ctl.tmem_base, 512);
     tmem_relinquish();
   }
-  for (int i = threadIdx.x; i < 256 * 32; i += kCmpThreads) lists[i] = make_uint2(0u, 0u);
+  for (int i = threadIdx.x; i < 256 * kListStride; i += kCmpThreads) lists[i] = make_uint2(0u, 0u);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -190,14 +203,14 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       auto issue_qk = [&](int t, int s) {
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + t * 128, umma_desc_sw128(sbase + kOffQ + t * kTileBytes + ks * 32),
+          umma_ss(tmem + kColS + t * 128, umma_desc_sw128(sbase + kOffQ + t * kTileBytes + ks * 32),
                   umma_desc_sw128(sbase + kOffK + s * kTileBytes + ks * 32), idesc_qk, ks > 0);
       };
       auto issue_pv = [&](int t, int s, bool acc) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tmem + 256 + t * 64, tmem + t * 128 + ks * 8, umma_desc_sw128(sbase + kOffV + s * kTileBytes + ks * 2048),
-                  idesc_pv, (acc || ks > 0) ? 1u : 0u);
+          umma_ts(tmem + kColO + t * 64, tmem + kColP + t * 64 + ks * 8,
+                  umma_desc_sw128(sbase + kOffV + s * kTileBytes + ks * 2048), idesc_pv, (acc || ks > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(&ctl.q_full, 0, abort_flag) && mbar_wait(&ctl.k_full[0], 0, abort_flag);
       if (ok) {
@@ -220,6 +233,9 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             issue_pv(t, s, j > 0);
             if (t == 1) umma_commit(&ctl.v_empty[s]);
             if (nxt) {
+              ok = mbar_wait(&ctl.tk_done[t], j & 1, abort_flag);    // S of this tile has been read by top-k too
+              if (!ok) break;
+              tc_fence_after();
               issue_qk(t, sn);
               umma_commit(&ctl.s_full[t]);
               if (t == 1) umma_commit(&ctl.k_empty[sn]);
@@ -233,35 +249,18 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         mbar_wait(&ctl.o_full, 0, &dummy);     // let issued MMAs drain before tensor memory is freed
       }
     }
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------------ softmax + top-k, thread = row
+  } else if (warp >= 4 && warp < 12) {
+    // ------------------------------------------------------------------ softmax, thread = row
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;
-    const int row_local = t * 128 + quarter * 32 + lane;      // 0..255 inside the CTA
-    const int grow = q0 + row_local;
-    uint2* warp_lists = lists + (t * 128 + quarter * 32) * 32;
-    uint2* warp_pend = pends + (t * 128 + quarter * 32) * kPend;
-    uint2* my_pend = warp_pend + lane * kPend;
-    const uint32_t t_s = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + t * 128;
-    const uint32_t t_o = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + 256 + t * 64;
+    const int grow = q0 + t * 128 + quarter * 32 + lane;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t t_s = lane_base + kColS + t * 128;
+    const uint32_t t_o = lane_base + kColO + t * 64;
+    const uint32_t t_p = lane_base + kColP + t * 64;
     const float cs = p.c_scale;
-    float m_used = -INFINITY, l = 0.f, thr = -INFINITY;
-    int cnt = 0;
+    float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-
-    // merge the pending buffers of the rows in `mask` into their sorted lists
-    auto flush_rows = [&](uint32_t mask) {
-      while (mask) {
-        const int src = __ffs(mask) - 1;
-        mask &= mask - 1;
-        const int m = __shfl_sync(0xffffffffu, cnt, src);
-        const uint32_t kth = topk_flush_row(warp_lists + src * 32, warp_pend + src * kPend, m, lane, p.topk);
-        if (lane == src) {
-          cnt = 0;
-          thr = key_to_float(kth);
-        }
-      }
-    };
 
     for (int j = 0; j < ntiles; ++j) {
       if (!mbar_wait_warp(&ctl.s_full[t], j & 1, abort_flag)) { ok = false; break; }
@@ -269,37 +268,27 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const int col0 = j * 128;
       const bool tail = (col0 + 128 > p.Nc);
 
-      // pass 1: row maximum of the raw logits + top-k candidates
+      // pass 1: row maximum of the raw logits
       float rmax = -INFINITY;
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t x[32];
         tmem_ld32(t_s + c4 * 32, x);
         tmem_ld_wait();
-        int nvalid = 32;
         if (tail) {
-          nvalid = min(32, max(0, p.Nc - (col0 + c4 * 32)));
+          const int nvalid = min(32, max(0, p.Nc - (col0 + c4 * 32)));
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (i >= nvalid) x[i] = 0xff800000u;   // -inf
         }
+        float m4[4];
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          float cm = __uint_as_float(x[hf * 16]);
+        for (int q = 0; q < 4; ++q) {
+          m4[q] = __uint_as_float(x[q]);
 #pragma unroll
-          for (int i = 1; i < 16; ++i) cm = fmaxf(cm, __uint_as_float(x[hf * 16 + i]));
-          rmax = fmaxf(rmax, cm);
-          const bool hot = (cm >= thr);
-          if (!(p.flags & 2) && __any_sync(0xffffffffu, hot)) {
-            int e_start = hot ? 0 : 16;
-            while (true) {
-              topk_append16(x + hf * 16, col0 + c4 * 32 + hf * 16, nvalid - hf * 16, thr, my_pend, cnt, e_start);
-              const uint32_t fullmask = __ballot_sync(0xffffffffu, e_start < 16);
-              if (!fullmask) break;
-              flush_rows(fullmask);
-            }
-          }
+          for (int i = 1; i < 8; ++i) m4[q] = fmaxf(m4[q], __uint_as_float(x[q + 4 * i]));
         }
+        rmax = fmaxf(rmax, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
       }
 
       // exponent offset; rescale O only when the maximum moved by more than 2^8
@@ -327,7 +316,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_st_wait();
       }
 
-      // pass 2: P = exp2(s*c - m), row sum, bf16 P back over the S columns
+      // pass 2: P = exp2(s*c - m), row sum, bf16 P to its own tensor-memory columns
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -348,7 +337,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ls[i & 3] += p0 + p1;
           pk[i] = pack_bf16(p0, p1);
         }
-        tmem_st16(t_s + c4 * 16, pk);
+        tmem_st16(t_p + c4 * 16, pk);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_st_wait();
@@ -356,7 +345,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_arrive(&ctl.p_full[t]);
     }
 
-    // epilogue: O / l, lse, and the sorted index rows
+    // epilogue: O / l and lse
     if (ok) ok = mbar_wait_warp(&ctl.o_full, 0, abort_flag);
     if (ok) {
       tc_fence_after();
@@ -377,14 +366,86 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                                 pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
         }
       }
-      flush_rows(__ballot_sync(0xffffffffu, cnt > 0));
+    }
+    if (!ok && lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+  } else if (warp >= 12) {
+    // ------------------------------------------------------------------ top-k, thread = row
+    const int t = (warp - 12) >> 2;
+    const int quarter = warp & 3;
+    const uint32_t t_s = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kColS + t * 128;
+    uint2* warp_lists = lists + (t * 128 + quarter * 32) * kListStride;
+    uint2* my_row = warp_lists + lane * kListStride;
+    const int topk = p.topk;
+    const bool skip = (p.flags & 2) != 0;
+    float thr = -INFINITY;
+    bool ok = true;
+
+    for (int j = 0; j < ntiles; ++j) {
+      if (!mbar_wait_warp(&ctl.s_full[t], j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int col0 = j * 128;
+      const bool tail = (col0 + 128 > p.Nc);
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t x[32];
+        tmem_ld32(t_s + c4 * 32, x);
+        tmem_ld_wait();
+        if (c4 == 3) {                      // S has been read in full: the next Q K^T may overwrite it
+          tc_fence_before();
+          mbar_arrive(&ctl.tk_done[t]);
+        }
+        if (skip) continue;
+        int nvalid = 32;
+        if (tail) {
+          nvalid = min(32, max(0, p.Nc - (col0 + c4 * 32)));
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i >= nvalid) x[i] = 0xff800000u;   // -inf
+        }
+        const int cbase = col0 + c4 * 32;
+        if (j < kEarlyTiles) {
+          // dense phase: every thread serves its own row
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(x[i]);
+            if (i < nvalid && v > thr) {
+              topk_insert_own(my_row, sortable_key(v), static_cast<uint32_t>(cbase + i));
+              thr = key_to_float(my_row[topk - 1].x);
+            }
+          }
+        } else {
+          // sparse phase: maxima of groups of 4, then of 16, steer the scan
+          float g4[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            g4[q] = fmaxf(fmaxf(__uint_as_float(x[4 * q]), __uint_as_float(x[4 * q + 1])),
+                          fmaxf(__uint_as_float(x[4 * q + 2]), __uint_as_float(x[4 * q + 3])));
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const float g16 = fmaxf(fmaxf(g4[4 * hf], g4[4 * hf + 1]), fmaxf(g4[4 * hf + 2], g4[4 * hf + 3]));
+            if (__any_sync(0xffffffffu, g16 > thr)) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const bool hot = g4[4 * hf + q] > thr;
+                if (__any_sync(0xffffffffu, hot))
+                  topk_scan4(x + 16 * hf + 4 * q, cbase + 16 * hf + 4 * q, nvalid - (16 * hf + 4 * q), hot, thr,
+                             warp_lists, lane, topk);
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+
+    // sorted index rows: slot l is rank l; an empty slot decodes to column Nc-1
+    if (ok) {
       __syncwarp();
       const int wrow0 = q0 + t * 128 + quarter * 32;
-      // the lists are sorted: slot l is rank l; an empty slot decodes to column Nc-1
       for (int r = 0; r < 32 && wrow0 + r < p.Nq; ++r) {
-        const uint2 ent = warp_lists[r * 32 + lane];
-        if (lane < p.topk)
-          p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * p.topk + lane] =
+        const uint2 ent = warp_lists[r * kListStride + lane];
+        if (lane < topk)
+          p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * topk + lane] =
               (ent.x == 0u) ? (p.Nc - 1) : static_cast<int32_t>(ent.y);
       }
     }

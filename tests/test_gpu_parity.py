@@ -92,6 +92,19 @@ def test_cmp_attn_topk_seeded(B, H, Nq, Nc, topk, variant):
     _cmp_case(q, k, v, topk, variant=variant, what=f"seeded {Nq}x{Nc}/v{variant}")
 
 
+def test_cmp_attn_all_equal_scores():
+    """Rows whose logits are all equal (a zero query): the table is columns 0..K-1 in order, and a
+    row of equal scores must not slow the scan down (every column ties with the threshold)."""
+    from speed3r_b200 import ops
+    B, H, Nq, Nc, K = 1, 2, 300, 2000, 32
+    q = torch.zeros(B, H, Nq, 64)
+    q[:, :, ::2] = randn(81, B, H, (Nq + 1) // 2, 64)          # odd rows stay zero
+    k, v = randn(82, B, H, Nc, 64), randn(83, B, H, Nc, 64)
+    _cmp_case(q, k, v, K, what="equal-scores")
+    _, _, idx = ops._cmp_fwd(dev(q), dev(k), dev(v), K, 0.125)
+    assert torch.equal(idx[:, :, 1::2].cpu(), torch.arange(K, dtype=torch.int32).expand(B, H, Nq // 2, K))
+
+
 def test_cmp_attn_large_logits_and_rescale():
     """Row maxima that grow along the key axis force the lazy O rescale path."""
     B, H, N = 1, 2, 1024
