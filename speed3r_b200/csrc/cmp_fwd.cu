@@ -42,7 +42,9 @@ constexpr int kOffQ = 0;
 constexpr int kOffK = 2 * kTileBytes;
 constexpr int kOffV = kOffK + kStages * kTileBytes;
 constexpr int kOffL = kOffV + kStages * kTileBytes;
-constexpr int kCmpSmemBytes = kOffL + kListBytes + 1024;
+constexpr int kScratchBytes = 8 * 16 * 32 * 4;          // per top-k warp: 16 logits x 32 lanes
+constexpr int kOffScr = kOffL + kListBytes;
+constexpr int kCmpSmemBytes = kOffScr + kScratchBytes + 1024;
 // tensor-memory columns
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 
@@ -76,52 +78,56 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
 }
 
 // Thread-local insertion into this thread's own row (sorted, 32 slots): shift worse entries down.
+// The position (number of kept keys >= the new key) comes from a 5-step binary search; the shift is
+// then a run of independent load/store pairs rather than a compare-and-move chain.
 __device__ __noinline__ void topk_insert_own(uint2* row, uint32_t key, uint32_t column) {
   if (key <= row[31].x) return;                // an equal key loses to the older, smaller column
-  int s = 31;
-  while (s > 0) {
-    const uint2 prev = row[s - 1];
-    if (prev.x >= key) break;
-    row[s] = prev;
-    --s;
-  }
-  row[s] = make_uint2(key, column);
+  int pos = 0;
+#pragma unroll
+  for (int step = 16; step >= 1; step >>= 1)
+    if (row[pos + step - 1].x >= key) pos += step;     // slots [0,pos) hold keys >= key; pos <= 31
+#pragma unroll 4
+  for (int s = 31; s > pos; --s) row[s] = row[s - 1];
+  row[pos] = make_uint2(key, column);
 }
 
 // Warp-cooperative insertion into the row `list_row` (lane l owns slot l).  The insert position is
 // the number of kept keys >= the new key; lanes at and below it shift down by one.
 // Returns the key in slot topk-1 afterwards (0 while fewer than topk real entries exist).
-__device__ __forceinline__ uint32_t topk_insert_coop(uint2* list_row, int lane, int topk, float score, int column) {
-  const uint32_t key = sortable_key(score);
-  uint2 ent = list_row[lane];
+// `ent` is this lane's slot of the row being updated, held in a register across the row's hits.
+__device__ __forceinline__ void topk_insert_coop(uint2& ent, int lane, int topk, uint32_t key, uint32_t column) {
   const int pos = __popc(__ballot_sync(0xffffffffu, ent.x >= key));
   if (pos < topk) {                                   // warp-uniform
     const uint32_t up_k = __shfl_up_sync(0xffffffffu, ent.x, 1);
     const uint32_t up_c = __shfl_up_sync(0xffffffffu, ent.y, 1);
     if (lane >= pos) {
       ent.x = (lane == pos) ? key : up_k;
-      ent.y = (lane == pos) ? static_cast<uint32_t>(column) : up_c;
-      list_row[lane] = ent;
+      ent.y = (lane == pos) ? column : up_c;
     }
   }
-  return __shfl_sync(0xffffffffu, ent.x, topk - 1);
 }
 
-// Four consecutive logits of this thread's row: ballot the hits and insert them one by one.
-__device__ __forceinline__ void topk_scan4(const uint32_t* x, int col0, int nvalid, bool hot, float& thr,
-                                           uint2* warp_lists, int lane, int topk) {
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float v = __uint_as_float(x[e]);
-    const bool cand = hot && (e < nvalid) && (v > thr);
-    uint32_t mask = __ballot_sync(0xffffffffu, cand);
-    while (mask) {
-      const int src = __ffs(mask) - 1;
-      mask &= mask - 1;
-      const float sv = __shfl_sync(0xffffffffu, v, src);
-      const uint32_t kth = topk_insert_coop(warp_lists + src * kListStride, lane, topk, sv, col0 + e);
-      if (lane == src) thr = key_to_float(kth);
+// Sparse phase, 16 consecutive logits per thread.  `m` is this thread's hit mask (bit i: x[i] >
+// thr), `any` the ballot of threads with hits.  The chunk's values have been published in
+// `scratch` ([i/4][lane] as uint4) so that every lane can read the hit's score.  Rows are served
+// one at a time; a row's list is loaded once, takes all of the row's hits, and is stored once.
+__device__ __noinline__ void topk_serve_hits(uint32_t any, uint32_t m, const uint32_t* scratch, int col0, float& thr,
+                                             uint2* warp_lists, int lane, int topk) {
+  while (any) {
+    const int src = __ffs(any) - 1;
+    any &= any - 1;
+    uint32_t ms = __shfl_sync(0xffffffffu, m, src);
+    uint2* row = warp_lists + src * kListStride;
+    uint2 ent = row[lane];
+    while (ms) {
+      const int e = __ffs(ms) - 1;
+      ms &= ms - 1;
+      const float v = __uint_as_float(scratch[(((e >> 2) * 32 + src) << 2) + (e & 3)]);
+      topk_insert_coop(ent, lane, topk, sortable_key(v), static_cast<uint32_t>(col0 + e));
     }
+    row[lane] = ent;
+    const uint32_t kth = __shfl_sync(0xffffffffu, ent.x, topk - 1);
+    if (lane == src) thr = key_to_float(kth);
   }
 }
 
@@ -375,6 +381,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t t_s = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kColS + t * 128;
     uint2* warp_lists = lists + (t * 128 + quarter * 32) * kListStride;
     uint2* my_row = warp_lists + lane * kListStride;
+    uint32_t* scratch = reinterpret_cast<uint32_t*>(sptr + kOffScr) + (warp - 12) * (16 * 32);
     const int topk = p.topk;
     const bool skip = (p.flags & 2) != 0;
     float thr = -INFINITY;
@@ -386,52 +393,49 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const int col0 = j * 128;
       const bool tail = (col0 + 128 > p.Nc);
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t x[32];
-        tmem_ld32(t_s + c4 * 32, x);
+      for (int c8 = 0; c8 < 8; ++c8) {
+        uint32_t x[16];
+        tmem_ld16(t_s + c8 * 16, x);
         tmem_ld_wait();
-        if (c4 == 3) {                      // S has been read in full: the next Q K^T may overwrite it
+        if (c8 == 7) {                      // S has been read in full: the next Q K^T may overwrite it
           tc_fence_before();
           mbar_arrive(&ctl.tk_done[t]);
         }
         if (skip) continue;
-        int nvalid = 32;
+        const int cbase = col0 + c8 * 16;
         if (tail) {
-          nvalid = min(32, max(0, p.Nc - (col0 + c4 * 32)));
+          const int nvalid = min(16, max(0, p.Nc - cbase));
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i >= nvalid) x[i] = 0xff800000u;   // -inf
+          for (int i = 0; i < 16; ++i)
+            if (i >= nvalid) x[i] = 0xff800000u;   // -inf never exceeds a threshold
         }
-        const int cbase = col0 + c4 * 32;
         if (j < kEarlyTiles) {
           // dense phase: every thread serves its own row
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const float v = __uint_as_float(x[i]);
-            if (i < nvalid && v > thr) {
+            if (v > thr) {
               topk_insert_own(my_row, sortable_key(v), static_cast<uint32_t>(cbase + i));
               thr = key_to_float(my_row[topk - 1].x);
             }
           }
         } else {
-          // sparse phase: maxima of groups of 4, then of 16, steer the scan
-          float g4[8];
+          // sparse phase: branch-free hit mask, one vote per chunk, hits served by the whole warp
+          uint32_t m0 = 0u, m1 = 0u;
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            g4[q] = fmaxf(fmaxf(__uint_as_float(x[4 * q]), __uint_as_float(x[4 * q + 1])),
-                          fmaxf(__uint_as_float(x[4 * q + 2]), __uint_as_float(x[4 * q + 3])));
+          for (int i = 0; i < 8; ++i) {
+            m0 |= (__uint_as_float(x[i]) > thr) ? (1u << i) : 0u;
+            m1 |= (__uint_as_float(x[8 + i]) > thr) ? (256u << i) : 0u;
+          }
+          const uint32_t m = m0 | m1;
+          const uint32_t any = __ballot_sync(0xffffffffu, m != 0u);
+          if (any) {
+            uint4* s4 = reinterpret_cast<uint4*>(scratch);
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            const float g16 = fmaxf(fmaxf(g4[4 * hf], g4[4 * hf + 1]), fmaxf(g4[4 * hf + 2], g4[4 * hf + 3]));
-            if (__any_sync(0xffffffffu, g16 > thr)) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const bool hot = g4[4 * hf + q] > thr;
-                if (__any_sync(0xffffffffu, hot))
-                  topk_scan4(x + 16 * hf + 4 * q, cbase + 16 * hf + 4 * q, nvalid - (16 * hf + 4 * q), hot, thr,
-                             warp_lists, lane, topk);
-              }
-            }
+            for (int q = 0; q < 4; ++q) s4[q * 32 + lane] = make_uint4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+            __syncwarp();
+            topk_serve_hits(any, m, scratch, cbase, thr, warp_lists, lane, topk);
+            __syncwarp();
           }
         }
       }
