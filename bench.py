@@ -210,13 +210,32 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)
     marks = []
 
+    def step_partitioned(q_, k_, v_, g_, record=False):
+        """N > 1: this rank's query blocks; events around the two attention kernels when recording."""
+        e = [ev() for _ in range(4)] if record else None
+
+        def cmp_fn(a, b, c, kk):
+            if record: e[0].record()
+            r = ops.flash_attn_topk_func(a, b, c, kk)
+            if record: e[1].record()
+            return r
+
+        def sel_fn(a, b, c, i, gt, oc, bs):
+            if record: e[2].record()
+            r = ops.sel_attn_merge_chunked(a, b, c, i, gt, oc, bs)
+            if record: e[3].record()
+            return r
+
+        y, _ = seq_parallel.sparse_attention_partitioned(q_, k_, v_, g_, BS, TOPK, ops.pool_tokens, cmp_fn, sel_fn,
+                                                         side_stream=side)
+        if record:
+            marks.append(e)
+        return y
+
     def step(record=False):
-        """Returns y; with record=True also appends per-kernel CUDA events (single GPU only)."""
+        """Returns y; with record=True also appends per-kernel CUDA events."""
         if world > 1:
-            y, _ = seq_parallel.sparse_attention_partitioned(
-                q, k, v, gate, BS, TOPK, ops.pool_tokens, lambda a, b, c, kk: ops.flash_attn_topk_func(a, b, c, kk),
-                lambda a, b, c, i, gt, oc, bs: ops.sel_attn_merge_chunked(a, b, c, i, gt, oc, bs), side_stream=side)
-            return y
+            return step_partitioned(q, k, v, gate, record)
         if bwd:
             ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
         else:
@@ -249,7 +268,7 @@ def main():
         s, e_ = ev(), ev()
         s.record()
         for _ in range(args.steps):
-            step(record=(world == 1))
+            step(record=True)
         e_.record()
         torch.cuda.synchronize()
         if world > 1:
@@ -271,6 +290,16 @@ def main():
 
     # per-kernel averages (single GPU): pooling, compression attention + top-k, selection + merge
     roof, kern = None, None
+    if world > 1 and marks and rank == 0:
+        # rank 0's share of the work: Nq/world query rows against all Nc pooled keys
+        avg = lambda i: sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)
+        t_cmp, t_sel = avg(0), avg(2)
+        ach = f_cmp / world / t_cmp / 1e9
+        kern = {"cmp_attn_topk_ms": t_cmp, "sel_attn_merge_ms": t_sel, "rank": 0,
+                "cmp_tflops_per_gpu": ach, "sel_tflops_per_gpu": f_sel / world / t_sel / 1e9}
+        roof = {"kernel": "cmp_fwd_kernel (compression attention + top-k), rank 0", "bound": "tensor", "achieved": ach,
+                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": None,
+                "peak_source": f"{peaks['src']} sustained bf16 (kernel timed inside a long step)"}
     if world == 1 and marks:
         avg = lambda i: sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)
         t_pool, t_cmp, t_sel = avg(0), avg(1), avg(2)
@@ -281,13 +310,19 @@ def main():
                 "cmp_tflops": f_cmp / t_cmp / 1e9, "sel_gather_gbs": sel_bytes / t_sel / 1e6,
                 "sel_frac_hbm": sel_bytes / t_sel / 1e6 / peaks["hbm_gbs"], "sel_tflops": f_sel / t_sel / 1e9}
         ach = f_cmp / t_cmp / 1e9
+        # DRAM traffic of one launch: ncu measured 38.8 MB read + 2.4 MB written for the 100-view case
+        # (profiles/cmp_fwd_kernel_100views.md); the kernel reads its inputs once and everything else hits
+        # L2, so traffic grows in proportion to the number of pooled rows.
+        traffic = 41.2e6 * (args.views / 100.0)
         roof = {"kernel": "cmp_fwd_kernel (compression attention + top-k)", "bound": "tensor", "achieved": ach,
-                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": None,
+                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": traffic,
+                "traffic_unit": "bytes/launch (ncu dram read+write at 100 views, scaled by views)",
                 "peak_source": f"{peaks['src']} sustained bf16 (kernel timed inside a long step)"}
 
     # end to end through the public op functions with HOST buffers (pinned), copies inside the timing
     e2e = None
-    if world == 1 and not args.no_e2e and not bwd:
+    if not args.no_e2e and not bwd:
+        # every rank moves its own shard: pinned host -> device, run, result back to pinned host
         hq, hk, hv, hg = (t.cpu().pin_memory() for t in (q, k, v, gate))
         hy = torch.empty(1, Tl, H * D, dtype=torch.bfloat16).pin_memory()
         dq_, dk_, dv_, dg_ = (torch.empty_like(t) for t in (q, k, v, gate))
@@ -295,14 +330,19 @@ def main():
         def e2e_step():
             dq_.copy_(hq, non_blocking=True); dk_.copy_(hk, non_blocking=True)
             dv_.copy_(hv, non_blocking=True); dg_.copy_(hg, non_blocking=True)
-            qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (dq_, dk_, dv_))
-            o_c, idx = ops.flash_attn_topk_func(qc, kc, vc, TOPK)
-            y = ops.sel_attn_merge(dq_, dk_, dv_, idx, dg_, o_c, BS)
+            if world > 1:
+                y = step_partitioned(dq_, dk_, dv_, dg_)
+            else:
+                qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (dq_, dk_, dv_))
+                o_c, idx = ops.flash_attn_topk_func(qc, kc, vc, TOPK)
+                y = ops.sel_attn_merge(dq_, dk_, dv_, idx, dg_, o_c, BS)
             hy.copy_(y, non_blocking=True)
 
         with torch.no_grad():
             e2e_step()
             torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
             n = max(2, min(args.steps, 5))
             s2, e2 = ev(), ev()
             s2.record()
@@ -310,10 +350,16 @@ def main():
                 e2e_step()
             e2.record()
             torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
         ems = s2.elapsed_time(e2) / n
+        if world > 1:
+            tms = torch.tensor([ems], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ems = tms.item()
         e2e = {"value": (f_cmp + f_sel) / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ems,
-               "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)),
-               "d2h_bytes_per_step": hy.numel() * hy.element_size()}
+               "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)),
+               "d2h_bytes_per_step": world * hy.numel() * hy.element_size()}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -332,7 +378,9 @@ def main():
                     steps=args.steps, warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong",
                     vs_baseline=None, dtype="bf16", data="synthetic", config=workload_config(args),
                     views_per_s=args.views / (ms * 1e-3), clocks=clocks, e2e=e2e,
-                    gpu_launches=args.steps * (5 if not bwd else 5 + 3 + 1 + 6 + 2 + 3),
+                    # own kernels per step and rank: 3 pool + compression attention + selection/merge
+                    # (+ with the backward: merge bwd, 4 CSR, 2 selection bwd, delta + 2 compression bwd, 3 pool bwd)
+                    gpu_launches=args.steps * world * (5 if not bwd else 5 + 1 + 4 + 2 + 3 + 3),
                     roofline=roof, kernels=kern, cpu_baseline=cpu)
         print(json.dumps(line))
     if world > 1:

@@ -35,9 +35,11 @@ def partition(T: int, block: int, world: int, rank: int) -> Tuple[int, int]:
 def all_gather_chunks(x: Tensor, group=None) -> Tensor:
     """``x [B,H,n,d]`` on every rank -> ``[G,B,H,n,d]`` (chunk g = rank g's tensor)."""
     world = dist.get_world_size(group)
-    out = torch.empty((world,) + tuple(x.shape), device=x.device, dtype=x.dtype)
+    # the output is laid out as the ranks' tensors concatenated along dim 0 (both NCCL and gloo
+    # accept this form); viewed as [G, ...] afterwards
+    out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), device=x.device, dtype=x.dtype)
     dist.all_gather_into_tensor(out, x.contiguous(), group=group)
-    return out
+    return out.view((world,) + tuple(x.shape))
 
 
 def chunks_to_dense(xc: Tensor) -> Tensor:
