@@ -113,3 +113,25 @@ def test_sortable_key_total_order():
     v = np.array([-np.inf, -3.5, -0.0, 0.0, 1e-30, 2.0, np.inf], dtype=np.float32)
     k = R.sortable_key(v)
     assert (np.diff(k.astype(np.int64)) > 0).all()
+
+
+def test_baseline_config1_op():
+    """BASELINE config 1 (B=1, T=2048 = 8 views x 256, 16 heads, d=64, seed 0, 16/16/16/32): the
+    restatement against the reference's kernels on the same regenerated inputs."""
+    g = golden("cfg1")
+    torch.manual_seed(0)
+    B, H, T, d, Bs, K = 1, 16, 2048, 64, 16, 32
+    q, k, v = torch.randn(B, H, T, d), torch.randn(B, H, T, d), torch.randn(B, H, T, d)
+    gate = torch.sigmoid(torch.randn(B, H, T, 2))
+    torch.testing.assert_close(q[0, 3, 100], g["q_probe"])          # the seed reproduces the fixture's inputs
+    torch.testing.assert_close(gate[0, 5, 77], g["gate_probe"])
+    q_c, k_c, v_c = (R.pool_tokens(t, Bs, Bs) for t in (q, k, v))
+    o_c, lse_c, idx = R.cmp_attn_topk(q_c, k_c, v_c, K)
+    assert torch.equal(idx, g["idx"].int())
+    torch.testing.assert_close(o_c, g["o_c"], **FP)
+    torch.testing.assert_close(lse_c, g["lse_c"], **FP)
+    o_s, lse_s = R.sel_attn(q, k, v, idx, Bs)
+    torch.testing.assert_close(o_s[:, :, ::8], g["o_s_sub"], **FP)
+    torch.testing.assert_close(lse_s, g["lse_s"], **FP)
+    y = R.gated_merge(gate, o_c, o_s, Bs)
+    torch.testing.assert_close(y[:, ::8], g["y_sub"], **FP)
