@@ -146,6 +146,25 @@ size_t s3r_csr_workspace_bytes(int B, int H, int Nq, int topk, int Nkb);
 int s3r_build_key_csr(const int32_t* idx, int32_t* offsets, int32_t* qids, int B, int H, int Nq, int topk,
                       int Nkb, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same index build with NO caller-provided workspace and no allocation of any kind.
+ * It has no counterpart in the reference.  It is for hosts that cannot allocate device memory
+ * when the call is made (all memory was handed to another runtime up front, or a cudaMalloc, which
+ * synchronises the device, is not acceptable where the call sits).  The scratch is a fixed buffer
+ * of S3R_CSR_STATIC_SCRATCH_BYTES inside the library image; every GPU that loads the library
+ * holds it until the process exits.
+ *   - Same arguments, outputs and ordering guarantees as s3r_build_key_csr.
+ *   - Tables whose scratch (s3r_csr_workspace_bytes) exceeds the buffer are refused with
+ *     S3R_ERR_TOO_LARGE and a message; nothing is launched.
+ *   - The first call on each device resolves the buffer's device address (cudaGetSymbolAddress
+ *     with that device current).  Make that first call during set-up, before any stream capture.
+ *   - All calls on a device share the one buffer, which keeps whatever the previous call left; the
+ *     kernels overwrite every slot they later read, so nothing needs clearing.  Two calls that
+ *     overlap on the GPU (different streams) race on it: serialise them.
+ *   - Calls cudaMemsetAsync on `offsets` and launches kernels; no cudaMalloc/cudaFree. */
+#define S3R_CSR_STATIC_SCRATCH_BYTES (8u << 20)
+int s3r_build_key_csr_static(const int32_t* idx, int32_t* offsets, int32_t* qids, int B, int H, int Nq,
+                             int topk, int Nkb, void* stream);
+
 /* Backward of the gated merge (autograd of sparse_attention.py:127-136), producing what the
  * selection backward needs in one pass over dy:
  *   dy [B,Tq,H*d] ; gate / o_c / o_s as in the forward

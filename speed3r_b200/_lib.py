@@ -28,6 +28,7 @@ SIGNATURES = {
                               _i, _i, _i, _i, _i, _i, _i, _f, _p]),
     "s3r_csr_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "s3r_build_key_csr": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p, _sz, _p]),
+    "s3r_build_key_csr_static": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "s3r_merge_bwd": (_i, [_p, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "s3r_delta": (_i, [_p, _p, _p, _i64, _i, _p]),
     "s3r_sel_attn_bwd": (_i, [_p] * 12 + [_i, _i, _i, _i, _i, _i, _i, _f, _p]),

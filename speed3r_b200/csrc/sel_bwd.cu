@@ -7,6 +7,8 @@
 // Both stream 16-row tiles through a two-stage cp.async ring private to the warp and use the
 // mma.sync building blocks of bwd_common.cuh.  They are bounded by gather bandwidth like the
 // forward (16..64 flop per byte).
+#include <mutex>
+
 #include "bwd_common.cuh"
 
 namespace s3r {
@@ -424,6 +426,50 @@ extern "C" int s3r_build_key_csr(const int32_t* idx, int32_t* offsets, int32_t* 
   csr_sort_kernel<<<static_cast<unsigned>((nseg * 32 + 255) / 256), 256, 0, st>>>(offsets, tmp, qids, per_bh, Nkb, nseg);
   S3R_CUDA(cudaGetLastError());
   return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same index build for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no allocator to ask: a plug-in running inside another runtime
+// that handed out all device memory at start-up, or a latency-critical loop in which a
+// cudaMalloc (which synchronises the device) is not acceptable.  For them the scratch of the
+// index build lives in the library image itself: a fixed array that every GPU that loads the
+// library keeps until the process exits.  Sizes whose scratch does not fit are refused.
+//
+// In host code the array's name is only a stand-in; its device address is obtained once per
+// device with cudaGetSymbolAddress (with that device current) and handed to the kernels.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_csr_static_scratch[S3R_CSR_STATIC_SCRATCH_BYTES];
+
+extern "C" int s3r_build_key_csr_static(const int32_t* idx, int32_t* offsets, int32_t* qids, int B, int H, int Nq,
+                                        int topk, int Nkb, void* stream) {
+  S3R_REQUIRE(idx && offsets && qids, S3R_ERR_NULL, "s3r_build_key_csr_static: NULL pointer");
+  S3R_REQUIRE(B > 0 && H > 0 && Nq > 0 && topk > 0 && Nkb > 0, S3R_ERR_SHAPE, "s3r_build_key_csr_static: bad sizes");
+  const size_t need = s3r_csr_workspace_bytes(B, H, Nq, topk, Nkb);
+  S3R_REQUIRE(need <= static_cast<size_t>(S3R_CSR_STATIC_SCRATCH_BYTES), S3R_ERR_TOO_LARGE,
+              "s3r_build_key_csr_static: this table needs %zu bytes of scratch, the built-in buffer holds %zu; "
+              "use s3r_build_key_csr with a caller-provided workspace",
+              need, static_cast<size_t>(S3R_CSR_STATIC_SCRATCH_BYTES));
+  // set-up, once per device: resolve the device address of the built-in buffer
+  static void* dev_ptr[64] = {};
+  static std::mutex mu;
+  int dev = -1;
+  S3R_CUDA(cudaGetDevice(&dev));
+  S3R_REQUIRE(dev >= 0 && dev < 64, S3R_ERR_UNSUPPORTED, "s3r_build_key_csr_static: device ordinal %d out of range", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_ptr[dev]) {
+      void* p = nullptr;
+      S3R_CUDA(cudaGetSymbolAddress(&p, g_csr_static_scratch));
+      dev_ptr[dev] = p;
+    }
+    scratch = dev_ptr[dev];
+  }
+  // Nothing in the scratch has to start at zero: the scan writes every cursor and the sort only reads
+  // the slots the fill wrote, so whatever an earlier call left behind is never read.
+  return s3r_build_key_csr(idx, offsets, qids, B, H, Nq, topk, Nkb, scratch, S3R_CSR_STATIC_SCRATCH_BYTES, stream);
 }
 
 extern "C" int s3r_delta(const void* o, const void* d_o, float* delta, int64_t rows, int d, void* stream) {
