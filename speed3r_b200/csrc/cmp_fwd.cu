@@ -20,31 +20,38 @@
 // threads themselves (each owns one TMEM lane).
 //
 // Top-k.  Per row, shared memory holds the best 32 entries (key(score), column), sorted, slot 0
-// best.  The row's threshold is the topk-th kept score.
-//   * first kEarlyTiles tiles (hits are dense): every thread inserts its own hits into its own
-//     row by shifting, all lanes in parallel;
-//   * afterwards (hits are rare): a thread finds hot groups of 4 columns from the maxima of its
-//     max tree; a hit is inserted by the whole warp with one ballot and one shuffle-up (lane l
-//     owns slot l of the row being updated).
+// best; the row's threshold is the topk-th kept score.  Everything is done by the row's own thread
+// so that the 32 rows of a warp proceed side by side (a warp-cooperative insert is a long chain of
+// dependent votes and shuffles that serves one row at a time):
+//   * per 16 columns a thread builds a branch-free hit mask against its threshold and moves its
+//     hits (key, column) into its row's small pending buffer;
+//   * the tile is released to the MMA pipeline as soon as it has been read;
+//   * every few tiles, or when a buffer fills, each thread merges its pending hits into its sorted
+//     list (binary search for the position, then a shift).  Batching keeps most lanes busy in that
+//     step; the threshold is refreshed there.
+// Lists and pending buffers are laid out [slot][lane] per warp, so thread-private accesses never
+// conflict on shared-memory banks whatever slots the lanes touch.
 // Ties on the score keep the smaller column first because columns arrive in ascending order.
 // Slots start empty (key 0), which decodes to column Nc-1, the reference's padding.
 #include "common.cuh"
 
 namespace s3r {
 
-constexpr int kCmpThreads = 640;
+constexpr int kCmpThreads = 640;             // 12 pipeline/softmax warps + 8 top-k warps
 constexpr int kTileBytes = 128 * 128;        // 128 rows x 64 bf16
-constexpr int kListStride = 33;              // entries per row: 32 + 1 of padding (bank spread)
-constexpr int kListBytes = 256 * kListStride * 8;
+constexpr int kListBytes = 256 * 32 * 8;      // 8 warps x [32 slots][32 lanes] x (key, column)
 constexpr int kStages = 3;
-constexpr int kEarlyTiles = 8;
+constexpr int kMergeEvery = 4;                // tiles between merges of the pending hits
 constexpr int kOffQ = 0;
 constexpr int kOffK = 2 * kTileBytes;
 constexpr int kOffV = kOffK + kStages * kTileBytes;
 constexpr int kOffL = kOffV + kStages * kTileBytes;
-constexpr int kScratchBytes = 8 * 16 * 32 * 4;          // per top-k warp: 16 logits x 32 lanes
+constexpr int kScratchBytes = 8 * 16 * 32 * 4;          // per top-k warp: 16 logits x 32 rows
 constexpr int kOffScr = kOffL + kListBytes;
-constexpr int kCmpSmemBytes = kOffScr + kScratchBytes + 1024;
+constexpr int kPend = 8;                                // pending hits per row between merges
+constexpr int kPendBytes = 256 * kPend * 8;
+constexpr int kOffPend = kOffScr + kScratchBytes;
+constexpr int kCmpSmemBytes = kOffPend + kPendBytes + 1024;
 // tensor-memory columns
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 
@@ -77,58 +84,28 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
   return __uint_as_float(b);
 }
 
-// Thread-local insertion into this thread's own row (sorted, 32 slots): shift worse entries down.
-// The position (number of kept keys >= the new key) comes from a 5-step binary search; the shift is
-// then a run of independent load/store pairs rather than a compare-and-move chain.
-__device__ __noinline__ void topk_insert_own(uint2* row, uint32_t key, uint32_t column) {
-  if (key <= row[31].x) return;                // an equal key loses to the older, smaller column
+// Insertion into this thread's own row.  `col` points at slot 0 of the row; slots are 32 entries
+// apart ([slot][lane] layout).  The position (number of kept keys >= the new key) comes from a
+// 5-step binary search; the shift is then a run of independent load/store pairs.
+__device__ __forceinline__ void topk_insert_own(uint2* col, uint32_t key, uint32_t column) {
+  if (key <= col[31 * 32].x) return;           // an equal key loses to the older, smaller column
   int pos = 0;
 #pragma unroll
   for (int step = 16; step >= 1; step >>= 1)
-    if (row[pos + step - 1].x >= key) pos += step;     // slots [0,pos) hold keys >= key; pos <= 31
+    if (col[(pos + step - 1) * 32].x >= key) pos += step;     // slots [0,pos) hold keys >= key; pos <= 31
 #pragma unroll 4
-  for (int s = 31; s > pos; --s) row[s] = row[s - 1];
-  row[pos] = make_uint2(key, column);
+  for (int s = 31; s > pos; --s) col[s * 32] = col[(s - 1) * 32];
+  col[pos * 32] = make_uint2(key, column);
 }
 
-// Warp-cooperative insertion into the row `list_row` (lane l owns slot l).  The insert position is
-// the number of kept keys >= the new key; lanes at and below it shift down by one.
-// Returns the key in slot topk-1 afterwards (0 while fewer than topk real entries exist).
-// `ent` is this lane's slot of the row being updated, held in a register across the row's hits.
-__device__ __forceinline__ void topk_insert_coop(uint2& ent, int lane, int topk, uint32_t key, uint32_t column) {
-  const int pos = __popc(__ballot_sync(0xffffffffu, ent.x >= key));
-  if (pos < topk) {                                   // warp-uniform
-    const uint32_t up_k = __shfl_up_sync(0xffffffffu, ent.x, 1);
-    const uint32_t up_c = __shfl_up_sync(0xffffffffu, ent.y, 1);
-    if (lane >= pos) {
-      ent.x = (lane == pos) ? key : up_k;
-      ent.y = (lane == pos) ? column : up_c;
-    }
+// Merge this thread's pending hits into its list and refresh its threshold.
+__device__ __noinline__ void topk_merge_own(uint2* my_list, const uint2* my_pend, int& cnt, float& thr, int topk) {
+  for (int i = 0; i < cnt; ++i) {
+    const uint2 h = my_pend[i * 32];
+    topk_insert_own(my_list, h.x, h.y);
   }
-}
-
-// Sparse phase, 16 consecutive logits per thread.  `m` is this thread's hit mask (bit i: x[i] >
-// thr), `any` the ballot of threads with hits.  The chunk's values have been published in
-// `scratch` ([i/4][lane] as uint4) so that every lane can read the hit's score.  Rows are served
-// one at a time; a row's list is loaded once, takes all of the row's hits, and is stored once.
-__device__ __noinline__ void topk_serve_hits(uint32_t any, uint32_t m, const uint32_t* scratch, int col0, float& thr,
-                                             uint2* warp_lists, int lane, int topk) {
-  while (any) {
-    const int src = __ffs(any) - 1;
-    any &= any - 1;
-    uint32_t ms = __shfl_sync(0xffffffffu, m, src);
-    uint2* row = warp_lists + src * kListStride;
-    uint2 ent = row[lane];
-    while (ms) {
-      const int e = __ffs(ms) - 1;
-      ms &= ms - 1;
-      const float v = __uint_as_float(scratch[(((e >> 2) * 32 + src) << 2) + (e & 3)]);
-      topk_insert_coop(ent, lane, topk, sortable_key(v), static_cast<uint32_t>(col0 + e));
-    }
-    row[lane] = ent;
-    const uint32_t kth = __shfl_sync(0xffffffffu, ent.x, topk - 1);
-    if (lane == src) thr = key_to_float(kth);
-  }
+  if (cnt > 0) thr = key_to_float(my_list[(topk - 1) * 32].x);
+  cnt = 0;
 }
 
 __global__ void __launch_bounds__(kCmpThreads, 1)
@@ -168,7 +145,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     tmem_alloc(&ctl.tmem_base, 512);
     tmem_relinquish();
   }
-  for (int i = threadIdx.x; i < 256 * kListStride; i += kCmpThreads) lists[i] = make_uint2(0u, 0u);
+  for (int i = threadIdx.x; i < 256 * 32; i += kCmpThreads) lists[i] = make_uint2(0u, 0u);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -274,77 +251,85 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const int col0 = j * 128;
       const bool tail = (col0 + 128 > p.Nc);
 
-      // pass 1: row maximum of the raw logits
-      float rmax = -INFINITY;
-#pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t x[32];
-        tmem_ld32(t_s + c4 * 32, x);
-        tmem_ld_wait();
-        if (tail) {
-          const int nvalid = min(32, max(0, p.Nc - (col0 + c4 * 32)));
+      // One pass with tensor-memory loads kept one chunk ahead of the arithmetic: P is computed
+      // with the exponent offset carried over from earlier tiles while the tile's maximum is
+      // gathered on the side.  Only if some row's maximum outgrew its offset by more than 2^8 is
+      // the tile redone with the new offset (O and l rescaled).  S stays valid until this
+      // warpgroup arrives on p_full, so the redo re-reads it.  Tile 0 has no offset yet: its
+      // maximum is taken first.
+      auto mask_tail = [&](uint32_t (&x)[16], int c8) {
+        const int nvalid = min(16, max(0, p.Nc - (col0 + c8 * 16)));
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i >= nvalid) x[i] = 0xff800000u;   // -inf
-        }
-        float m4[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          m4[q] = __uint_as_float(x[q]);
-#pragma unroll
-          for (int i = 1; i < 8; ++i) m4[q] = fmaxf(m4[q], __uint_as_float(x[q + 4 * i]));
-        }
-        rmax = fmaxf(rmax, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-      }
-
-      // exponent offset; rescale O only when the maximum moved by more than 2^8
-      const float mt = rmax * cs;
-      float factor = 1.f;
-      bool need = false;
+        for (int i = 0; i < 16; ++i)
+          if (i >= nvalid) x[i] = 0xff800000u;   // -inf
+      };
       if (j == 0) {
-        m_used = mt;
-      } else if (mt > m_used + 8.f) {
-        factor = fast_exp2(m_used - mt);
-        m_used = mt;
-        l *= factor;
-        need = true;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        float rmax0 = -INFINITY;
 #pragma unroll 1
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t o[32];
-          tmem_ld32(t_o + hf * 32, o);
+        for (int c8 = 0; c8 < 8; ++c8) {
+          uint32_t x[16];
+          tmem_ld16(t_s + c8 * 16, x);
           tmem_ld_wait();
+          if (tail) mask_tail(x, c8);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-          tmem_st32(t_o + hf * 32, o);
+          for (int i = 0; i < 16; ++i) rmax0 = fmaxf(rmax0, __uint_as_float(x[i]));
         }
-        tmem_st_wait();
+        m_used = rmax0 * cs;
       }
-
-      // pass 2: P = exp2(s*c - m), row sum, bf16 P to its own tensor-memory columns
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      float ls[4];
+      bool redo;
+      do {
+        ls[0] = ls[1] = ls[2] = ls[3] = 0.f;
+        float rm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        auto process = [&](uint32_t (&x)[16], int c8) {
+          if (tail) mask_tail(x, c8);
+          uint32_t pk[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float s0 = __uint_as_float(x[2 * i]), s1 = __uint_as_float(x[2 * i + 1]);
+            rm[i & 3] = fmaxf(rm[i & 3], fmaxf(s0, s1));
+            const float p0 = fast_exp2(fmaf(s0, cs, -m_used));
+            const float p1 = fast_exp2(fmaf(s1, cs, -m_used));
+            ls[i & 3] += p0 + p1;
+            pk[i] = pack_bf16(p0, p1);
+          }
+          tmem_st8(t_p + c8 * 8, pk);
+        };
+        uint32_t xa[16], xb[16];
+        tmem_ld16(t_s, xa);
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t x[32];
-        tmem_ld32(t_s + c4 * 32, x);
-        tmem_ld_wait();
-        if (tail) {
-          const int nvalid = min(32, max(0, p.Nc - (col0 + c4 * 32)));
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i >= nvalid) x[i] = 0xff800000u;
+        for (int c8 = 0; c8 < 8; c8 += 2) {
+          tmem_ld_wait();
+          tmem_ld16(t_s + (c8 + 1) * 16, xb);
+          process(xa, c8);
+          tmem_ld_wait();
+          if (c8 + 2 < 8) tmem_ld16(t_s + (c8 + 2) * 16, xa);
+          process(xb, c8 + 1);
         }
-        uint32_t pk[16];
+        const float mt = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3])) * cs;
+        const bool need = mt > m_used + 8.f;
+        redo = __any_sync(0xffffffffu, need);
+        if (redo) {
+          const float factor = need ? fast_exp2(m_used - mt) : 1.f;
+          if (need) {
+            m_used = mt;
+            l *= factor;
+          }
+          tmem_st_wait();
+          if (j > 0) {
+#pragma unroll 1
+            for (int hf = 0; hf < 2; ++hf) {
+              uint32_t o[32];
+              tmem_ld32(t_o + hf * 32, o);
+              tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), cs, -m_used));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(x[2 * i + 1]), cs, -m_used));
-          ls[i & 3] += p0 + p1;
-          pk[i] = pack_bf16(p0, p1);
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_st32(t_o + hf * 32, o);
+            }
+            tmem_st_wait();
+          }
         }
-        tmem_st16(t_p + c4 * 16, pk);
-      }
+      } while (redo);
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_st_wait();
       tc_fence_before();
@@ -379,9 +364,11 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int t = (warp - 12) >> 2;
     const int quarter = warp & 3;
     const uint32_t t_s = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kColS + t * 128;
-    uint2* warp_lists = lists + (t * 128 + quarter * 32) * kListStride;
-    uint2* my_row = warp_lists + lane * kListStride;
+    uint2* warp_lists = lists + (warp - 12) * (32 * 32);            // [slot][lane]
+    uint2* my_list = warp_lists + lane;
     uint32_t* scratch = reinterpret_cast<uint32_t*>(sptr + kOffScr) + (warp - 12) * (16 * 32);
+    uint2* my_pend = reinterpret_cast<uint2*>(sptr + kOffPend) + (warp - 12) * (kPend * 32) + lane;   // [i][lane]
+    int cnt = 0;
     const int topk = p.topk;
     const bool skip = (p.flags & 2) != 0;
     float thr = -INFINITY;
@@ -392,16 +379,9 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       tc_fence_after();
       const int col0 = j * 128;
       const bool tail = (col0 + 128 > p.Nc);
-#pragma unroll 1
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t x[16];
-        tmem_ld16(t_s + c8 * 16, x);
-        tmem_ld_wait();
-        if (c8 == 7) {                      // S has been read in full: the next Q K^T may overwrite it
-          tc_fence_before();
-          mbar_arrive(&ctl.tk_done[t]);
-        }
-        if (skip) continue;
+
+      auto handle = [&](uint32_t (&x)[16], int c8) {
+        if (skip) return;
         const int cbase = col0 + c8 * 16;
         if (tail) {
           const int nvalid = min(16, max(0, p.Nc - cbase));
@@ -409,36 +389,55 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int i = 0; i < 16; ++i)
             if (i >= nvalid) x[i] = 0xff800000u;   // -inf never exceeds a threshold
         }
-        if (j < kEarlyTiles) {
-          // dense phase: every thread serves its own row
+        // branch-free hit mask; a thread moves its own hits to its pending buffer
+        uint32_t m0 = 0u, m1 = 0u;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float v = __uint_as_float(x[i]);
-            if (v > thr) {
-              topk_insert_own(my_row, sortable_key(v), static_cast<uint32_t>(cbase + i));
-              thr = key_to_float(my_row[topk - 1].x);
-            }
-          }
-        } else {
-          // sparse phase: branch-free hit mask, one vote per chunk, hits served by the whole warp
-          uint32_t m0 = 0u, m1 = 0u;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            m0 |= (__uint_as_float(x[i]) > thr) ? (1u << i) : 0u;
-            m1 |= (__uint_as_float(x[8 + i]) > thr) ? (256u << i) : 0u;
-          }
-          const uint32_t m = m0 | m1;
-          const uint32_t any = __ballot_sync(0xffffffffu, m != 0u);
-          if (any) {
-            uint4* s4 = reinterpret_cast<uint4*>(scratch);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) s4[q * 32 + lane] = make_uint4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
-            __syncwarp();
-            topk_serve_hits(any, m, scratch, cbase, thr, warp_lists, lane, topk);
-            __syncwarp();
-          }
+        for (int i = 0; i < 8; ++i) {
+          m0 |= (__uint_as_float(x[i]) > thr) ? (1u << i) : 0u;
+          m1 |= (__uint_as_float(x[8 + i]) > thr) ? (256u << i) : 0u;
         }
+        uint32_t m = m0 | m1;
+        if (m) {
+          // this thread's own copy of the chunk, so that a hit can be fetched by its (dynamic) index
+          uint4* s4 = reinterpret_cast<uint4*>(scratch);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) s4[q * 32 + lane] = make_uint4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+        }
+        while (true) {
+          while (m && cnt < kPend) {
+            const int e = __ffs(m) - 1;
+            m &= m - 1;
+            const float v = __uint_as_float(scratch[(((e >> 2) * 32 + lane) << 2) + (e & 3)]);
+            my_pend[cnt * 32] = make_uint2(sortable_key(v), static_cast<uint32_t>(cbase + e));
+            ++cnt;
+          }
+          if (!__any_sync(0xffffffffu, m != 0u)) break;          // nobody ran out of room
+          topk_merge_own(my_list, my_pend, cnt, thr, topk);      // every lane merges what it has
+        }
+      };
+
+      // tensor-memory loads run one chunk ahead of the handling
+      uint32_t xa[16], xb[16];
+      tmem_ld16(t_s, xa);
+#pragma unroll 1
+      for (int c8 = 0; c8 < 8; c8 += 2) {
+        tmem_ld_wait();
+        tmem_ld16(t_s + (c8 + 1) * 16, xb);
+        handle(xa, c8);
+        tmem_ld_wait();
+        if (c8 + 2 < 8) {
+          tmem_ld16(t_s + (c8 + 2) * 16, xa);
+        } else {                              // S has been read in full: the next Q K^T may overwrite it
+          tc_fence_before();
+          mbar_arrive(&ctl.tk_done[t]);
+        }
+        handle(xb, c8 + 1);
       }
+      // the tile is already released; merge the pending hits every few tiles, or early when some
+      // buffer is nearly full
+      if (!skip && ((j % kMergeEvery) == kMergeEvery - 1 || j == ntiles - 1 ||
+                    __any_sync(0xffffffffu, cnt >= kPend - 2)))
+        topk_merge_own(my_list, my_pend, cnt, thr, topk);
       __syncwarp();
     }
 
@@ -447,7 +446,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       __syncwarp();
       const int wrow0 = q0 + t * 128 + quarter * 32;
       for (int r = 0; r < 32 && wrow0 + r < p.Nq; ++r) {
-        const uint2 ent = warp_lists[r * kListStride + lane];
+        const uint2 ent = warp_lists[lane * 32 + r];
         if (lane < topk)
           p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * topk + lane] =
               (ent.x == 0u) ? (p.Nc - 1) : static_cast<int32_t>(ent.y);
