@@ -85,17 +85,22 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
 }
 
 // Insertion into this thread's own row.  `col` points at slot 0 of the row; slots are 32 entries
-// apart ([slot][lane] layout).  The position (number of kept keys >= the new key) comes from a
-// 5-step binary search; the shift is then a run of independent load/store pairs.
+// apart ([slot][lane] layout).  One fully unrolled, predicated sweep from the bottom: every entry
+// worse than the newcomer moves down one slot, the newcomer lands above them.  All 31 loads are
+// independent (no search, no data-dependent loop), so the sweep pipelines and the lanes of a warp
+// never diverge, whatever their positions.  An equal key stays above the newcomer (it is older and
+// has the smaller column).
 __device__ __forceinline__ void topk_insert_own(uint2* col, uint32_t key, uint32_t column) {
-  if (key <= col[31 * 32].x) return;           // an equal key loses to the older, smaller column
-  int pos = 0;
+  const bool ins = key > col[31 * 32].x;       // otherwise it does not make the list
+  int moved = 0;                               // entries worse than the newcomer (a suffix of the list)
 #pragma unroll
-  for (int step = 16; step >= 1; step >>= 1)
-    if (col[(pos + step - 1) * 32].x >= key) pos += step;     // slots [0,pos) hold keys >= key; pos <= 31
-#pragma unroll 4
-  for (int s = 31; s > pos; --s) col[s * 32] = col[(s - 1) * 32];
-  col[pos * 32] = make_uint2(key, column);
+  for (int s = 31; s >= 1; --s) {
+    const uint2 prev = col[(s - 1) * 32];
+    const bool mv = ins && prev.x < key;       // independent of the other slots
+    if (mv) col[s * 32] = prev;
+    moved += mv ? 1 : 0;
+  }
+  if (ins) col[(31 - moved) * 32] = make_uint2(key, column);
 }
 
 // Merge this thread's pending hits into its list and refresh its threshold.
@@ -389,14 +394,27 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int i = 0; i < 16; ++i)
             if (i >= nvalid) x[i] = 0xff800000u;   // -inf never exceeds a threshold
         }
-        // branch-free hit mask; a thread moves its own hits to its pending buffer
-        uint32_t m0 = 0u, m1 = 0u;
+        // Branch-free hit mask.  The sweep runs from the last column to the first and keeps the
+        // value of the hit it saw last, i.e. of the FIRST hit in column order, so the common case
+        // (one hit in the chunk) is appended without any indexed access.  Hits must reach the
+        // pending buffer in ascending column order: that is what keeps equal scores in column order.
+        uint32_t m0 = 0u, m1 = 0u, hv0 = 0u, hv1 = 0u;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          m0 |= (__uint_as_float(x[i]) > thr) ? (1u << i) : 0u;
-          m1 |= (__uint_as_float(x[8 + i]) > thr) ? (256u << i) : 0u;
+        for (int i = 7; i >= 0; --i) {
+          const bool h0 = __uint_as_float(x[i]) > thr, h1 = __uint_as_float(x[8 + i]) > thr;
+          m0 |= h0 ? (1u << i) : 0u;
+          m1 |= h1 ? (256u << i) : 0u;
+          hv0 = h0 ? x[i] : hv0;
+          hv1 = h1 ? x[8 + i] : hv1;
         }
         uint32_t m = m0 | m1;
+        if (m != 0u && cnt < kPend) {
+          const int e = __ffs(m) - 1;
+          my_pend[cnt * 32] = make_uint2(sortable_key(__uint_as_float(m0 ? hv0 : hv1)), static_cast<uint32_t>(cbase + e));
+          ++cnt;
+          m &= m - 1;
+        }
+        if (!__any_sync(0xffffffffu, m != 0u)) return;             // nothing left anywhere in the warp
         if (m) {
           // this thread's own copy of the chunk, so that a hit can be fetched by its (dynamic) index
           uint4* s4 = reinterpret_cast<uint4*>(scratch);
@@ -435,7 +453,8 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       // the tile is already released; merge the pending hits every few tiles, or early when some
       // buffer is nearly full
-      if (!skip && ((j % kMergeEvery) == kMergeEvery - 1 || j == ntiles - 1 ||
+      const int merge_every = (p.flags >> 8) ? (p.flags >> 8) : kMergeEvery;
+      if (!skip && ((j % merge_every) == merge_every - 1 || j == ntiles - 1 ||
                     __any_sync(0xffffffffu, cnt >= kPend - 2)))
         topk_merge_own(my_list, my_pend, cnt, thr, topk);
       __syncwarp();
