@@ -292,7 +292,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float s0 = __uint_as_float(x[2 * i]), s1 = __uint_as_float(x[2 * i + 1]);
-            rm[i & 3] = fmaxf(rm[i & 3], fmaxf(s0, s1));
+            rm[i & 3] = fmax3(rm[i & 3], s0, s1);
             const float p0 = fast_exp2(fmaf(s0, cs, -m_used));
             const float p1 = fast_exp2(fmaf(s1, cs, -m_used));
             ls[i & 3] += p0 + p1;
@@ -392,27 +392,36 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const int nvalid = min(16, max(0, p.Nc - cbase));
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (i >= nvalid) x[i] = 0xff800000u;   // -inf never exceeds a threshold
+            if (i >= nvalid) x[i] = 0xff7fffffu;   // -FLT_MAX: never a hit, and 0 * it stays finite
         }
-        // Branch-free hit mask.  The sweep runs from the last column to the first and keeps the
-        // value of the hit it saw last, i.e. of the FIRST hit in column order, so the common case
-        // (one hit in the chunk) is appended without any indexed access.  Hits must reach the
-        // pending buffer in ascending column order: that is what keeps equal scores in column order.
-        uint32_t m0 = 0u, m1 = 0u, hv0 = 0u, hv1 = 0u;
+        // Hit mask on the FMA pipe (compares, selects and logic ops all share the half-rate ALU
+        // pipe, which this kernel saturates first):  t = saturate((x - thr) * 2^60) is 1.0 for a
+        // hit and 0.0 otherwise (the fused product is exact before rounding, so any x > thr gives
+        // >= 1);  sum t * 2^i is the mask, sum t * x the value of the hit when there is exactly
+        // one.  Chunks with several hits, or a full buffer, take the indexed path below, which
+        // appends in ascending column order (that is what keeps equal scores in column order).
+        // (2^90: exact for thresholds below 2^37 in magnitude and score gaps above 2^-90, i.e. for
+        // every pair of distinct fp32 logits larger than 2^-66 in magnitude.)
+        const float kHuge = 1.2379400392853803e27f;              // 2^90
+        const float nthr = -thr * kHuge;                         // +inf while the list has free slots
+        float acc0 = 0.f, acc1 = 0.f, hv0 = 0.f, hv1 = 0.f;
 #pragma unroll
-        for (int i = 7; i >= 0; --i) {
-          const bool h0 = __uint_as_float(x[i]) > thr, h1 = __uint_as_float(x[8 + i]) > thr;
-          m0 |= h0 ? (1u << i) : 0u;
-          m1 |= h1 ? (256u << i) : 0u;
-          hv0 = h0 ? x[i] : hv0;
-          hv1 = h1 ? x[8 + i] : hv1;
+        for (int i = 0; i < 8; ++i) {
+          const float a = __uint_as_float(x[i]), b = __uint_as_float(x[8 + i]);
+          const float t0 = __saturatef(fmaf(a, kHuge, nthr));
+          const float t1 = __saturatef(fmaf(b, kHuge, nthr));
+          acc0 = fmaf(t0, static_cast<float>(1u << i), acc0);
+          acc1 = fmaf(t1, static_cast<float>(256u << i), acc1);
+          hv0 = fmaf(t0, a, hv0);
+          hv1 = fmaf(t1, b, hv1);
         }
-        uint32_t m = m0 | m1;
-        if (m != 0u && cnt < kPend) {
-          const int e = __ffs(m) - 1;
-          my_pend[cnt * 32] = make_uint2(sortable_key(__uint_as_float(m0 ? hv0 : hv1)), static_cast<uint32_t>(cbase + e));
+        uint32_t m = __float2uint_rn(acc0 + acc1);
+        const float hv = hv0 + hv1;
+        // (a zero or non-finite sum goes the indexed way: the sum cannot tell -0.0 from +0.0)
+        if (m != 0u && (m & (m - 1u)) == 0u && cnt < kPend && hv != 0.f && fabsf(hv) < INFINITY) {
+          my_pend[cnt * 32] = make_uint2(sortable_key(hv), static_cast<uint32_t>(cbase + __ffs(m) - 1));
           ++cnt;
-          m &= m - 1;
+          m = 0u;
         }
         if (!__any_sync(0xffffffffu, m != 0u)) return;             // nothing left anywhere in the warp
         if (m) {

@@ -67,6 +67,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// max of three in one instruction (three-operand max of sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Order-preserving float -> uint32 map: flip every bit of a negative value, set the sign bit of
 // a non-negative one.  Larger float <=> larger key; -0.0 < +0.0.
 __device__ __forceinline__ uint32_t sortable_key(float v) {
