@@ -403,7 +403,9 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // (2^90: exact for thresholds below 2^37 in magnitude and score gaps above 2^-90, i.e. for
         // every pair of distinct fp32 logits larger than 2^-66 in magnitude.)
         const float kHuge = 1.2379400392853803e27f;              // 2^90
-        const float nthr = -thr * kHuge;                         // +inf while the list has free slots
+        // while the list has free slots (thr = -inf) every real score is a hit, the -FLT_MAX fillers
+        // of the tail are not: a large finite offset does both (an infinite one would not)
+        const float nthr = (thr == -INFINITY) ? 3.0e38f : -thr * kHuge;
         float acc0 = 0.f, acc1 = 0.f, hv0 = 0.f, hv1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
