@@ -52,7 +52,12 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons while the GPU runs the workload.
+
+    nvidia-smi needs about a second before its first row, so the sampler is started before the warm-up and
+    every row carries its arrival time; `stop(t0, t1)` reports the rows that fell inside the timed region
+    and, when that region was too short to catch two, the rows of the whole loaded window
+    (`hold()` keeps the same step running, untimed, until enough rows have arrived)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -63,7 +68,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -71,9 +76,12 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def count_since(self, t0):
+        return sum(1 for t, _ in self.rows if t >= t0)
+
+    def stop(self, t0, t1, t_hold):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -81,9 +89,14 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        inside = [r for t, r in self.rows if t0 <= t <= t1]
+        window = "timed region"
+        if len(inside) < 2:
+            inside = [r for t, r in self.rows if t0 <= t <= t_hold]
+            window = "timed region + the same step repeated untimed right after it"
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in inside:
             try:
                 sm.append(float(r[1]))
                 mx = float(r[2])
@@ -94,7 +107,7 @@ class ClockSampler:
                 pass
         busy = [x for x in sm if mx and x > 0]
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -256,24 +269,38 @@ def main():
 
     ctx = torch.enable_grad() if bwd else torch.no_grad()
     with ctx:
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
         for _ in range(args.warmup):
             step()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
         torch.cuda.synchronize()
         s, e_ = ev(), ev()
+        t0 = time.time()
         s.record()
         for _ in range(args.steps):
             step(record=True)
         e_.record()
         torch.cuda.synchronize()
+        t1 = time.time()
         if world > 1:
             dist.barrier()
-        clocks = sampler.stop() if rank == 0 else None
+        # a timed region shorter than the sampler's period: keep the same load on, untimed, until it has rows
+        hold = torch.zeros(1, device=dev)
+        while True:
+            if rank == 0:
+                need = sampler.proc is not None and sampler.count_since(t0) < 3 and time.time() - t1 < 3.0
+                hold.fill_(1.0 if need else 0.0)
+            if world > 1:
+                dist.broadcast(hold, 0)
+            if hold.item() == 0.0:
+                break
+            step()
+            torch.cuda.synchronize()
+        clocks = sampler.stop(t0, t1, time.time()) if rank == 0 else None
         ms = s.elapsed_time(e_) / args.steps
     if world > 1:
         tms = torch.tensor([ms], device=dev)
@@ -325,17 +352,21 @@ def main():
         # every rank moves its own shard: pinned host -> device, run, result back to pinned host
         hq, hk, hv, hg = (t.cpu().pin_memory() for t in (q, k, v, gate))
         hy = torch.empty(1, Tl, H * D, dtype=torch.bfloat16).pin_memory()
-        dq_, dk_, dv_, dg_ = (torch.empty_like(t) for t in (q, k, v, gate))
+        if world > 1:
+            dq_, dk_, dv_, dg_ = (torch.empty_like(t) for t in (q, k, v, gate))
+
+        pipe = None
+        if world == 1:
+            from speed3r_b200.host_pipeline import HostPipeline
+            pipe = HostPipeline(H, T, D, BS, TOPK, device=dev)
 
         def e2e_step():
+            if pipe is not None:          # copies overlapped with the kernels on three streams
+                pipe(hq, hk, hv, hg, hy)
+                return
             dq_.copy_(hq, non_blocking=True); dk_.copy_(hk, non_blocking=True)
             dv_.copy_(hv, non_blocking=True); dg_.copy_(hg, non_blocking=True)
-            if world > 1:
-                y = step_partitioned(dq_, dk_, dv_, dg_)
-            else:
-                qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (dq_, dk_, dv_))
-                o_c, idx = ops.flash_attn_topk_func(qc, kc, vc, TOPK)
-                y = ops.sel_attn_merge(dq_, dk_, dv_, idx, dg_, o_c, BS)
+            y = step_partitioned(dq_, dk_, dv_, dg_)
             hy.copy_(y, non_blocking=True)
 
         with torch.no_grad():
@@ -359,7 +390,9 @@ def main():
             ems = tms.item()
         e2e = {"value": (f_cmp + f_sel) / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ems,
                "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)),
-               "d2h_bytes_per_step": world * hy.numel() * hy.element_size()}
+               "d2h_bytes_per_step": world * hy.numel() * hy.element_size(),
+               "api": ("speed3r_b200.HostPipeline (K/V by head group, queries by chunk, copies overlapped with kernels)"
+                       if pipe is not None else "speed3r_b200.seq_parallel.sparse_attention_partitioned on this rank's shard")}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
