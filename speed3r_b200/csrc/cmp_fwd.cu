@@ -19,19 +19,20 @@
 // maximum grows by more than 2^8, and only then is O rescaled in tensor memory, by the softmax
 // threads themselves (each owns one TMEM lane).
 //
-// Top-k.  Per row, shared memory holds the best 32 entries (key(score), column), sorted, slot 0
-// best; the row's threshold is the topk-th kept score.  Everything is done by the row's own thread
-// so that the 32 rows of a warp proceed side by side (a warp-cooperative insert is a long chain of
-// dependent votes and shuffles that serves one row at a time):
+// Top-k.  Per row, shared memory holds the best 32 entries (key(score), ~column) as a binary min-heap
+// whose root is the worst kept entry; the row's threshold is the root's score.  Everything is done by
+// the row's own thread so that the 32 rows of a warp proceed side by side (a warp-cooperative insert
+// is a long chain of dependent votes and shuffles that serves one row at a time):
 //   * per 16 columns a thread builds a branch-free hit mask against its threshold and moves its
 //     hits (key, column) into its row's small pending buffer;
 //   * the tile is released to the MMA pipeline as soon as it has been read;
-//   * every few tiles, or when a buffer fills, each thread merges its pending hits into its sorted
-//     list (binary search for the position, then a shift).  Batching keeps most lanes busy in that
-//     step; the threshold is refreshed there.
-// Lists and pending buffers are laid out [slot][lane] per warp, so thread-private accesses never
+//   * every few tiles, or when a buffer fills, each thread merges its pending hits into its heap
+//     (replace the root, sink at most five levels, in lockstep across the warp) and refreshes its
+//     threshold.  Batching keeps most lanes busy in that step;
+//   * at the end each thread heap-sorts its row in place: slot 0 is rank 0.
+// Heaps and pending buffers are laid out [slot][lane] per warp, so thread-private accesses never
 // conflict on shared-memory banks whatever slots the lanes touch.
-// Ties on the score keep the smaller column first because columns arrive in ascending order.
+// Ties on the score keep the smaller column first: the heap orders (score, ~column) as one 64-bit word.
 // Slots start empty (key 0), which decodes to column Nc-1, the reference's padding.
 #include "common.cuh"
 
@@ -84,32 +85,59 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
   return __uint_as_float(b);
 }
 
-// Insertion into this thread's own row.  `col` points at slot 0 of the row; slots are 32 entries
-// apart ([slot][lane] layout).  One fully unrolled, predicated sweep from the bottom: every entry
-// worse than the newcomer moves down one slot, the newcomer lands above them.  All 31 loads are
-// independent (no search, no data-dependent loop), so the sweep pipelines and the lanes of a warp
-// never diverge, whatever their positions.  An equal key stays above the newcomer (it is older and
-// has the smaller column).
-__device__ __forceinline__ void topk_insert_own(uint2* col, uint32_t key, uint32_t column) {
-  const bool ins = key > col[31 * 32].x;       // otherwise it does not make the list
-  int moved = 0;                               // entries worse than the newcomer (a suffix of the list)
+// A row's best entries live in a binary MIN-heap of `size` 64-bit words (key(score) << 32 | ~column) in
+// the row's own shared-memory column ([slot][lane] layout: whatever slots the 32 lanes touch, they never
+// meet on a bank).  The root is the worst kept entry, i.e. the row's threshold.  A newcomer replaces the
+// root and sinks: at most five levels for 32 entries, executed in lockstep by the 32 rows of a warp (a
+// settled lane idles through the remaining levels), ~16 shared-memory accesses instead of the ~62 of a
+// shift through a sorted list.  With ~column in the low half a larger word is a better entry under the
+// reference's order (score descending, column ascending), so one 64-bit compare decides everything.
+__device__ __forceinline__ uint64_t heap_ld(const uint2* p) {
+  const uint2 v = *p;
+  return (static_cast<uint64_t>(v.x) << 32) | v.y;
+}
+__device__ __forceinline__ void heap_st(uint2* p, uint64_t v) {
+  *p = make_uint2(static_cast<uint32_t>(v >> 32), static_cast<uint32_t>(v));
+}
+// Puts `v` in the root's place and restores the heap property over h[0..size).
+__device__ __forceinline__ void heap_sift_root(uint2* h, uint64_t v, int size, bool active) {
+  int i = 0;
+  bool go = active;
 #pragma unroll
-  for (int s = 31; s >= 1; --s) {
-    const uint2 prev = col[(s - 1) * 32];
-    const bool mv = ins && prev.x < key;       // independent of the other slots
-    if (mv) col[s * 32] = prev;
-    moved += mv ? 1 : 0;
+  for (int level = 0; level < 5; ++level) {
+    const int l = 2 * i + 1, r = l + 1;
+    uint64_t cl = ~0ull, cr = ~0ull;
+    if (go && l < size) cl = heap_ld(h + l * 32);
+    if (go && r < size) cr = heap_ld(h + r * 32);
+    const bool right = cr < cl;
+    const uint64_t c = right ? cr : cl;
+    const bool mv = go && c < v;
+    if (mv) heap_st(h + i * 32, c);
+    i = mv ? (right ? r : l) : i;
+    go = mv;
   }
-  if (ins) col[(31 - moved) * 32] = make_uint2(key, column);
+  if (active) heap_st(h + i * 32, v);
+}
+// Heap sort in place: afterwards slot 0 holds the best entry, slot size-1 the worst.
+__device__ __forceinline__ void heap_sort_desc(uint2* h, int size) {
+  for (int end = size - 1; end >= 1; --end) {
+    const uint64_t last = heap_ld(h + end * 32);
+    const uint64_t root = heap_ld(h);
+    heap_st(h + end * 32, root);          // the smallest of h[0..end] goes to the back
+    heap_sift_root(h, last, end, true);
+  }
 }
 
-// Merge this thread's pending hits into its list and refresh its threshold.
+// Merge this thread's pending hits (key, column; ascending columns) into its heap and refresh its threshold.
 __device__ __noinline__ void topk_merge_own(uint2* my_list, const uint2* my_pend, int& cnt, float& thr, int topk) {
   for (int i = 0; i < cnt; ++i) {
     const uint2 h = my_pend[i * 32];
-    topk_insert_own(my_list, h.x, h.y);
+    const uint64_t ent = (static_cast<uint64_t>(h.x) << 32) | (~h.y);
+    // strictly better than the worst kept entry (an equal score arrives with a larger column: it loses)
+    const bool want = ent > heap_ld(my_list);
+    heap_sift_root(my_list, ent, topk, want);
   }
-  if (cnt > 0) thr = key_to_float(my_list[(topk - 1) * 32].x);
+  if (cnt > 0) thr = key_to_float(my_list[0].x);
   cnt = 0;
 }
 
@@ -473,13 +501,14 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     // sorted index rows: slot l is rank l; an empty slot decodes to column Nc-1
     if (ok) {
+      heap_sort_desc(my_list, topk);
       __syncwarp();
       const int wrow0 = q0 + t * 128 + quarter * 32;
       for (int r = 0; r < 32 && wrow0 + r < p.Nq; ++r) {
         const uint2 ent = warp_lists[lane * 32 + r];
         if (lane < topk)
           p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * topk + lane] =
-              (ent.x == 0u) ? (p.Nc - 1) : static_cast<int32_t>(ent.y);
+              (ent.x == 0u) ? (p.Nc - 1) : static_cast<int32_t>(~ent.y);
       }
     }
     if (!ok && lane == 0) atomicOr(p.status, kStatusWaitTimeout);
