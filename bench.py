@@ -184,6 +184,7 @@ def main():
     ap.add_argument("--mode", default="fwd", choices=["fwd", "fwdbwd"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--module", action="store_true", help="also time the whole attention module at this size")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 5:
@@ -400,6 +401,39 @@ def main():
                "api": ("speed3r_b200.HostPipeline (K/V by head group, queries by chunk, copies overlapped with kernels)"
                        if pipe is not None else "speed3r_b200.seq_parallel.sparse_attention_partitioned on this rank's shard")}
 
+    # The whole module (qkv/gate/proj GEMMs + prologue + the op) at the same sequence length, forward, no
+    # gradients: once with the one-pass prologue kernel, once with the separate PyTorch steps around the op.
+    module = None
+    if world == 1 and not bwd and args.module:
+        import speed3r_b200
+        del q, k, v, gate
+        if not args.no_e2e:
+            del pipe, hq, hk, hv, hg, hy
+        torch.cuda.empty_cache()
+        dim = H * D
+        mod = speed3r_b200.SparseFlashAttentionRope(dim, num_heads=H, qkv_bias=True, proj_bias=True, qk_norm=True,
+                                                    rope=speed3r_b200.RoPE2D(100.0)).to(dev).eval()
+        gm = torch.Generator(device=dev).manual_seed(7)
+        x = torch.randn(1, T, dim, device=dev, generator=gm).bfloat16()
+        side = int(math.sqrt(TOK_PER_VIEW))            # token grid of one view, for plausible (y,x) positions
+        tok = torch.arange(T, device=dev) % TOK_PER_VIEW
+        xpos = torch.stack((tok // (TOK_PER_VIEW // side), tok % (TOK_PER_VIEW // side)), -1)[None].contiguous()
+
+        def time_module(fused):
+            mod._can_fuse_prologue = (lambda *a, **k_: False) if not fused else type(mod)._can_fuse_prologue.__get__(mod)
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                mod(x, xpos=xpos)
+                torch.cuda.synchronize()
+                a, b_ = ev(), ev()
+                a.record()
+                for _ in range(2):
+                    mod(x, xpos=xpos)
+                b_.record()
+                torch.cuda.synchronize()
+            return a.elapsed_time(b_) / 2
+        module = {"tokens": T, "dim": dim, "fused_prologue_ms": time_module(True), "separate_steps_ms": time_module(False)}
+        del mod, x
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cstep, cfl, sample, cores = cpu_sample(args.views)
@@ -421,6 +455,8 @@ def main():
                     # (+ with the backward: merge bwd, 4 CSR, 2 selection bwd, delta + 2 compression bwd, 3 pool bwd)
                     gpu_launches=args.steps * world * (5 if not bwd else 5 + 1 + 4 + 2 + 3 + 3),
                     roofline=roof, kernels=kern, cpu_baseline=cpu)
+        if module is not None:
+            line["module"] = module
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -70,6 +70,26 @@ int s3r_pool_bwd(const void* d_out, void* d_in, int64_t stride_b, int64_t stride
                  int B, int H, int T, int d, int kernel, int stride, int accumulate, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Prologue of the module in one pass over the packed projection.  Replaces the PyTorch code between
+ * `qkv = self.qkv(x)` and the two attention calls of SparseFlashAttentionRope.forward
+ * (pi3/models/layers/sparse_attention.py:95-123): F.avg_pool1d of the raw q,k,v, q_norm/k_norm
+ * (nn.LayerNorm over the head dimension, fp32 under autocast, result rounded to bf16), the 2-D
+ * rotary embedding RoPE2D (pi3/models/layers/pos_embed.py:112-159) at the token positions and at
+ * the truncated mean position of every block, and the `[B,N,3,H,d] -> 3 x [B,H,N,d]` split.
+ *   qkv            : [B,N,3,H,d] bf16, contiguous (the output of the qkv Linear)
+ *   pos            : [B,N,2] int64 (y,x) or NULL (no rotary embedding)
+ *   cos_tab/sin_tab: [tab_rows, d/2] bf16, row p = cos/sin of bf16(p * inv_freq) duplicated over the two
+ *                    halves (what RoPE2D caches); positions are clamped to the table
+ *   q_weight..k_bias: fp32 [d] LayerNorm affine parameters, or all NULL (Identity norms)
+ *   q,k,v          : [B,H,N,d] bf16 out;  q_c,k_c,v_c : [B,H,N/block,d] bf16 out
+ * N must be a multiple of `block`; d = 64; at most 42 heads.  Forward only: a caller that
+ * needs gradients runs the separate steps (s3r_pool_fwd/bwd and its own LayerNorm and rotary code). */
+int s3r_qkv_prologue_fwd(const void* qkv, const int64_t* pos, const void* cos_tab, const void* sin_tab,
+                         int tab_rows, const float* q_weight, const float* q_bias, const float* k_weight,
+                         const float* k_bias, float eps, void* q, void* k, void* v, void* q_c, void* k_c,
+                         void* v_c, int B, int H, int N, int d, int block, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Compression attention with fused top-k block selection.
  * Replaces flash_attn_topk_func / FlashAttnTopkFunc.forward / forward_with_topk /
  * _fwd_kernel_with_topk (pi3/models/sparse_attn/flash_attention_topk.py:22-200, 633-650) and

@@ -41,7 +41,16 @@ namespace s3r {
 constexpr int kCmpThreads = 640;             // 12 pipeline/softmax warps + 8 top-k warps
 constexpr int kTileBytes = 128 * 128;        // 128 rows x 64 bf16
 constexpr int kListBytes = 256 * 32 * 8;      // 8 warps x [32 slots][32 lanes] x (key, column)
-constexpr int kStages = 3;
+#ifndef S3R_CMP_STAGES
+#define S3R_CMP_STAGES 3
+#endif
+#ifndef S3R_CMP_PEND
+#define S3R_CMP_PEND 8
+#endif
+#ifndef S3R_CMP_PEND_SLACK
+#define S3R_CMP_PEND_SLACK 2
+#endif
+constexpr int kStages = S3R_CMP_STAGES;
 constexpr int kMergeEvery = 4;                // tiles between merges of the pending hits
 constexpr int kOffQ = 0;
 constexpr int kOffK = 2 * kTileBytes;
@@ -49,7 +58,7 @@ constexpr int kOffV = kOffK + kStages * kTileBytes;
 constexpr int kOffL = kOffV + kStages * kTileBytes;
 constexpr int kScratchBytes = 8 * 16 * 32 * 4;          // per top-k warp: 16 logits x 32 rows
 constexpr int kOffScr = kOffL + kListBytes;
-constexpr int kPend = 8;                                // pending hits per row between merges
+constexpr int kPend = S3R_CMP_PEND;                                // pending hits per row between merges
 constexpr int kPendBytes = 256 * kPend * 8;
 constexpr int kOffPend = kOffScr + kScratchBytes;
 constexpr int kCmpSmemBytes = kOffPend + kPendBytes + 1024;
@@ -494,7 +503,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // buffer is nearly full
       const int merge_every = (p.flags >> 8) ? (p.flags >> 8) : kMergeEvery;
       if (!skip && ((j % merge_every) == merge_every - 1 || j == ntiles - 1 ||
-                    __any_sync(0xffffffffu, cnt >= kPend - 2)))
+                    __any_sync(0xffffffffu, cnt >= kPend - S3R_CMP_PEND_SLACK)))
         topk_merge_own(my_list, my_pend, cnt, thr, topk);
       __syncwarp();
     }

@@ -69,6 +69,56 @@ def _(x, kernel, stride):
     return x.new_empty(B, H, (T - kernel) // stride + 1, d)
 
 
+def qkv_prologue(qkv: Tensor, num_heads: int, block: int, pos: Optional[Tensor] = None,
+                 cos: Optional[Tensor] = None, sin: Optional[Tensor] = None,
+                 q_norm: Optional[Tuple[Tensor, Tensor, float]] = None,
+                 k_norm: Optional[Tuple[Tensor, Tensor, float]] = None):
+    """Everything between the qkv projection and the two attention calls of the module
+    (pi3/models/layers/sparse_attention.py:95-123) in one kernel, forward only:
+    ``qkv [B,N,3*H*d]`` -> ``(q, k, v [B,H,N,d], q_c, k_c, v_c [B,H,N/block,d])`` with the per-head
+    LayerNorm of q and k (``(weight, bias, eps)`` or None), the 2-D rotary embedding at ``pos
+    [B,N,2]`` (``cos``/``sin`` = the bf16 tables RoPE2D caches) and, for the pooled tensors, at each
+    block's truncated mean position."""
+    _need(qkv, "qkv")
+    if qkv.requires_grad and torch.is_grad_enabled():
+        raise RuntimeError("qkv_prologue is forward-only; run the separate steps when gradients are needed")
+    B, N, C3 = qkv.shape[0], qkv.shape[1], qkv.numel() // (qkv.shape[0] * qkv.shape[1])
+    d = C3 // (3 * num_heads)
+    if C3 != 3 * num_heads * d or N % block:
+        raise RuntimeError(f"qkv_prologue: qkv {tuple(qkv.shape)} does not split into 3 x {num_heads} heads, "
+                           f"or N={N} is not a multiple of the block {block}")
+    if (q_norm is None) != (k_norm is None):
+        raise RuntimeError("qkv_prologue: q_norm and k_norm come together or not at all")
+    dev = qkv.device
+    f32 = lambda t: t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    qw = qb = kw = kb = None
+    eps = 1e-5
+    if q_norm is not None:
+        if abs(q_norm[2] - k_norm[2]) > 0:
+            raise RuntimeError("qkv_prologue: q_norm and k_norm must share eps")
+        qw, qb, kw, kb, eps = f32(q_norm[0]), f32(q_norm[1]), f32(k_norm[0]), f32(k_norm[1]), float(q_norm[2])
+    rows = 0
+    if pos is not None:
+        _need(cos, "cos")
+        _need(sin, "sin")
+        if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != d // 2:
+            raise RuntimeError(f"qkv_prologue: cos/sin tables must be [rows,{d // 2}]")
+        if tuple(pos.shape) != (B, N, 2) or pos.device != dev:
+            raise RuntimeError(f"qkv_prologue: pos must be [B,N,2] = {(B, N, 2)} on {dev}")
+        pos = pos.to(torch.int64).contiguous()
+        rows = cos.shape[0]
+    mk = lambda n: torch.empty(B, num_heads, n, d, device=dev, dtype=qkv.dtype)
+    q, k, v = mk(N), mk(N), mk(N)
+    q_c, k_c, v_c = mk(N // block), mk(N // block), mk(N // block)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().s3r_qkv_prologue_fwd(
+            qkv.data_ptr(), _ptr(pos), _ptr(cos) if pos is not None else 0, _ptr(sin) if pos is not None else 0, rows,
+            _ptr(qw), _ptr(qb), _ptr(kw), _ptr(kb), eps, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), B, num_heads, N, d, block, _stream()),
+            "s3r_qkv_prologue_fwd")
+    return q, k, v, q_c, k_c, v_c
+
+
 @torch.library.custom_op("speed3r_b200::pool_bwd", mutates_args=())
 def _pool_bwd(d_out: Tensor, T: int, kernel: int, stride: int) -> Tensor:
     _need(d_out, "d_out")

@@ -4,9 +4,11 @@
 ``q_norm``, ``k_norm``, ``gate`` = Sequential(Linear, Sigmoid)), attributes and ``forward(x,
 attn_bias=None, xpos=None)`` of pi3/models/layers/sparse_attention.py:60-141, so a checkpoint of
 the reference loads unchanged and ``BlockRope(attn_class=SparseFlashAttentionRope)`` works
-(pi3/models/layers/block.py:282-312).  The projections, LayerNorms and the rotary embedding stay
-PyTorch host code; pooling, the compression attention with its top-k selection, the selection
-attention and the gated merge run in the CUDA library (speed3r_b200.ops).
+(pi3/models/layers/block.py:282-312).  The projections stay PyTorch (cuBLAS) code; pooling, the compression attention with its top-k
+selection, the selection attention and the gated merge run in the CUDA library (speed3r_b200.ops).
+Without gradients the LayerNorms, the rotary embedding, the pooling and the q/k/v split run as one
+library kernel as well (``ops.qkv_prologue``); with gradients they stay PyTorch code around the
+differentiable ops.
 
 The reference's literals (pooling 16/16, top-k 32) are keyword arguments here with the same
 defaults.
@@ -105,6 +107,36 @@ class SparseFlashAttentionRope(nn.Module):
         self.record_idx = False      # debugging aid: keep the last selected-block table in .last_idx
         self.last_idx = None
 
+    def _can_fuse_prologue(self, qkv, x, xpos, N, Bs, d) -> bool:
+        """Inference (nothing to differentiate), norms that are LayerNorm(d) with affine or Identity, the
+        rotary module of this package or none, whole blocks, head counts the kernel takes."""
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            return False
+        norms = (self.q_norm, self.k_norm)
+        ident = all(isinstance(m, nn.Identity) for m in norms)
+        ln = all(isinstance(m, nn.LayerNorm) and m.elementwise_affine and m.bias is not None and
+                 tuple(m.normalized_shape) == (d,) for m in norms)
+        if not (ident or (ln and self.q_norm.eps == self.k_norm.eps)):
+            return False
+        if xpos is not None and not isinstance(self.rope, RoPE2D):
+            return False
+        return d == 64 and N % Bs == 0 and self.num_heads <= 42
+
+    def _forward_fused(self, qkv, gate, xpos, B, N, H, d, Bs) -> Tensor:
+        cos = sin = None
+        if xpos is not None:
+            cos, sin = self.rope._cos_sin(d // 2, self.rope._seq_len(xpos), qkv.device, qkv.dtype)
+        qn = kn = None
+        if isinstance(self.q_norm, nn.LayerNorm):
+            qn = (self.q_norm.weight, self.q_norm.bias, self.q_norm.eps)
+            kn = (self.k_norm.weight, self.k_norm.bias, self.k_norm.eps)
+        q, k, v, q_c, k_c, v_c = ops.qkv_prologue(qkv.detach(), H, Bs, xpos, cos, sin, qn, kn)
+        o_c, idx = ops.flash_attn_topk_func(q_c, k_c, v_c, self.topk)
+        if self.record_idx:
+            self.last_idx = idx.detach()
+        y = ops.sel_attn_merge(q, k, v, idx, gate, o_c, Bs)
+        return self.proj_drop(self.proj(y))
+
     def forward(self, x: Tensor, attn_bias=None, xpos: Optional[Tensor] = None) -> Tensor:
         B, N, C = x.shape
         H = self.num_heads
@@ -116,6 +148,8 @@ class SparseFlashAttentionRope(nn.Module):
             raise RuntimeError("SparseFlashAttentionRope runs in bf16 (use torch.autocast(dtype=torch.bfloat16)); "
                                f"got {qkv.dtype}")
         gate = gate.to(qkv.dtype)
+        if self._can_fuse_prologue(qkv, x, xpos, N, Bs, d):
+            return self._forward_fused(qkv, gate, xpos, B, N, H, d, Bs)
         qkv5 = qkv.view(B, N, 3, H, d)
         q_t, k_t, v_t = (qkv5[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # [B,H,N,d] views of the projection
 

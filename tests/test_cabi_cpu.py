@@ -53,6 +53,15 @@ def test_argument_errors_are_reported_without_a_gpu(lib):
     assert rc == -2 and "topk" in _lib.last_error()
     rc = lib.s3r_sel_attn_fwd(p, p, p, 1, 0, p, p, None, None, 0, 0, 0, None, None, 1, 1, 64, 64, 64, 48, 8, 0.125, None)
     assert rc == -2 and "block" in _lib.last_error()
+    # prologue: NULL output, ragged sequence, head count, LayerNorm parameters only in part, positions without tables
+    pro = lambda **kw: lib.s3r_qkv_prologue_fwd(
+        kw.get("qkv", p), kw.get("pos"), kw.get("cos"), kw.get("sin"), kw.get("rows", 0), kw.get("qw"), kw.get("qb"),
+        kw.get("kw"), kw.get("kb"), 1e-5, p, p, p, p, p, kw.get("v_c", p), 1, kw.get("H", 4), kw.get("N", 32), 64, 16, None)
+    assert pro(v_c=None) == -4
+    assert pro(N=40) == -1 and "multiple" in _lib.last_error()
+    assert pro(H=43) == -2 and "heads" in _lib.last_error()
+    assert pro(qw=p) == -4
+    assert pro(pos=p) == -4 and "tables" in _lib.last_error()
     # merge arguments must come together
     rc = lib.s3r_sel_attn_fwd(p, p, p, 1, 0, p, p, None, p, 0, 0, 0, None, None, 1, 1, 64, 64, 64, 16, 8, 0.125, None)
     assert rc == -4

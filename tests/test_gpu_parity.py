@@ -378,6 +378,68 @@ def test_module_forward_golden():
     assert same > 0.85, f"only {same:.2%} of the selected blocks agree with the fp32 selection"
 
 
+@pytest.mark.parametrize("with_norm,with_pos,H,Bs", [(True, True, 16, 16), (False, True, 2, 16), (True, False, 5, 4)])
+def test_qkv_prologue_matches_separate_steps(with_norm, with_pos, H, Bs):
+    """The one-pass prologue against the module's separate PyTorch steps (LayerNorm under autocast, RoPE2D in
+    bf16, the pooling kernel): v and its block means bit-equal; q, k and their pooled forms equal up to the
+    last bf16 bit of the LayerNorm (different fp32 summation order)."""
+    import speed3r_b200
+    from speed3r_b200 import ops
+    B, N, d = 2, 16 * 24, 64
+    g = torch.Generator(device=DEV).manual_seed(5)
+    qkv = (torch.randn(B, N, 3 * H * d, device=DEV, generator=g) * 1.5 + 0.3).bfloat16()
+    pos = torch.randint(0, 37, (B, N, 2), device=DEV, generator=g) if with_pos else None
+    rope = speed3r_b200.RoPE2D(100.0)
+    qn = torch.nn.LayerNorm(d).to(DEV) if with_norm else torch.nn.Identity()
+    kn = torch.nn.LayerNorm(d).to(DEV) if with_norm else torch.nn.Identity()
+    if with_norm:
+        with torch.no_grad():
+            for m in (qn, kn):
+                m.weight.copy_(1 + 0.2 * torch.randn(d, device=DEV, generator=g))
+                m.bias.copy_(0.1 * torch.randn(d, device=DEV, generator=g))
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        q_t, k_t, v_t = (qkv.view(B, N, 3, H, d)[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        q_c, k_c, v_c = (ops.pool_tokens(t, Bs, Bs) for t in (q_t, k_t, v_t))
+        q_c, k_c = qn(q_c).to(qkv.dtype), kn(k_c).to(qkv.dtype)
+        q, k = qn(q_t).to(qkv.dtype), kn(k_t).to(qkv.dtype)
+        if with_pos:
+            pos_c = pos.view(B, N // Bs, Bs, 2).float().mean(dim=2).int()
+            q_c, k_c, q, k = rope(q_c, pos_c), rope(k_c, pos_c), rope(q, pos), rope(k, pos)
+        cos = sin = None
+        if with_pos:
+            cos, sin = rope._cos_sin(d // 2, rope._seq_len(pos), qkv.device, qkv.dtype)
+        norms = ((qn.weight, qn.bias, qn.eps), (kn.weight, kn.bias, kn.eps)) if with_norm else (None, None)
+        fq, fk, fv, fqc, fkc, fvc = ops.qkv_prologue(qkv, H, Bs, pos, cos, sin, norms[0], norms[1])
+    assert torch.equal(fv, v_t.contiguous()) and torch.equal(fvc, v_c)
+    for name, a, b in (("q", fq, q), ("k", fk, k), ("q_c", fqc, q_c), ("k_c", fkc, k_c)):
+        assert a.shape == b.shape, name
+        same = (a == b).float().mean().item()
+        assert same > (0.98 if with_norm else 0.9999), f"{name}: only {same:.4%} of the elements are bit-equal"
+        assert_bf16_close(a, b.float(), name, max_abs=4e-2, mean_abs=1e-3)
+
+
+def test_module_forward_without_grad_uses_fused_prologue_and_matches():
+    """Under no_grad the module runs the one-pass prologue; its output equals the grad-enabled path's up to
+    bf16 rounding, and agrees with the oracle as the other path does."""
+    g = golden("module_fwd")
+    m, sd, heads = _module_pair(g)
+    m.record_idx = True
+    x, xpos = g["x"].to(DEV), g["xpos"].to(DEV)
+    assert m._can_fuse_prologue(torch.empty(0), x, xpos, x.shape[1], m.block_size ** 2, x.shape[-1] // heads) is False
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y_sep = m(x, xpos=xpos)
+        idx_sep = m.last_idx.cpu()
+        with torch.no_grad():
+            assert m._can_fuse_prologue(torch.empty(0), x, xpos, x.shape[1], m.block_size ** 2, x.shape[-1] // heads)
+            y = m(x, xpos=xpos)
+    idx = m.last_idx.cpu()
+    y_ref, _ = R.module_forward(sd, g["x"], g["xpos"], heads, return_aux=True, idx_override=idx)
+    assert_bf16_close(y, y_ref, "module y (fused prologue)", max_abs=6e-2, mean_abs=8e-3)
+    same = (torch.sort(idx, -1).values == torch.sort(idx_sep, -1).values).float().mean().item()
+    assert same > 0.97, f"only {same:.2%} of the selected blocks agree between the two prologues"
+    assert_bf16_close(y, y_sep.detach().float(), "fused vs separate", max_abs=6e-2, mean_abs=4e-3)
+
+
 def test_module_backward_golden():
     g = golden("module_bwd")
     m, sd, heads = _module_pair(g)
