@@ -36,11 +36,11 @@ struct alignas(16) Vec8 {
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-// LayerNorm over the 64 channels held by 8 lanes (8 each), fp32, two passes; result rounded to bf16.
+// LayerNorm over the 64 channels held by 8 lanes (8 each), fp32, two passes; the caller rounds to bf16.
 // `gmask` names the 8 lanes of the row: rows of one warp may belong to different tensors (q, k or v) and
 // take different paths, so every shuffle synchronises its own group only.
-__device__ __forceinline__ void ln_row(float (&x)[8], const float* __restrict__ w, const float* __restrict__ b,
-                                       int c0, float eps, uint32_t gmask) {
+__device__ __forceinline__ void ln_row(float (&x)[8], const float (&w)[8], const float (&b)[8], float eps,
+                                       uint32_t gmask) {
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) s += x[i];
@@ -56,30 +56,39 @@ __device__ __forceinline__ void ln_row(float (&x)[8], const float* __restrict__ 
   v += __shfl_xor_sync(gmask, v, 4);
   const float rstd = rsqrtf(v * (1.f / 64.f) + eps);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) x[i] = bf16r(fmaf((x[i] - mean) * rstd, __ldg(w + c0 + i), __ldg(b + c0 + i)));
+  for (int i = 0; i < 8; ++i) x[i] = fmaf((x[i] - mean) * rstd, w[i], b[i]);   // rounded to bf16 when packed
 }
 
-// 2-D rotary embedding of a row held by 8 lanes: lanes 0-3 hold the y half (32 channels), lanes 4-7 the x
-// half; inside a half channel j pairs with j+16, i.e. lane l with lane l^2.
-// out = bf16(bf16(t*cos) + bf16(rot*sin)),  rot = -t[j+16] for j < 16 and t[j-16] otherwise.
-__device__ __forceinline__ void rope_row(float (&x)[8], const __nv_bfloat16* __restrict__ cos_tab,
+// 2-D rotary embedding of a row held by 8 lanes, on packed bf16 pairs: lanes 0-3 hold the y half (32
+// channels), lanes 4-7 the x half; inside a half channel j pairs with j+16, i.e. lane l with lane l^2.
+// out = bf16(bf16(t*cos) + bf16(rot*sin)),  rot = -t[j+16] for j < 16 and t[j-16] otherwise: the packed
+// bf16 multiply and add (the _rn forms, which the compiler may not contract into one FMA) round exactly
+// where the reference's bf16 tensor ops do.
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ void rope_row(uint32_t (&xw)[4], const __nv_bfloat16* __restrict__ cos_tab,
                                          const __nv_bfloat16* __restrict__ sin_tab, int row, int l8,
                                          uint32_t gmask) {
   const Vec8 c = *reinterpret_cast<const Vec8*>(cos_tab + static_cast<int64_t>(row) * 32 + (l8 & 3) * 8);
   const Vec8 s = *reinterpret_cast<const Vec8*>(sin_tab + static_cast<int64_t>(row) * 32 + (l8 & 3) * 8);
-  const bool low = (l8 & 2) == 0;
+  const uint32_t flip = (l8 & 2) == 0 ? 0x80008000u : 0u;
 #pragma unroll
   for (int wd = 0; wd < 4; ++wd) {
-    const uint32_t mine = pack_bf16(x[2 * wd], x[2 * wd + 1]);          // exact: x is bf16-valued
-    const uint32_t other = __shfl_xor_sync(gmask, mine, 2);
-    const float r0 = low ? -bf16_lo(other) : bf16_lo(other);
-    const float r1 = low ? -bf16_hi(other) : bf16_hi(other);
-    x[2 * wd] = bf16r(bf16r(x[2 * wd] * bf16_lo(c.w[wd])) + bf16r(r0 * bf16_lo(s.w[wd])));
-    x[2 * wd + 1] = bf16r(bf16r(x[2 * wd + 1] * bf16_hi(c.w[wd])) + bf16r(r1 * bf16_hi(s.w[wd])));
+    const uint32_t other = __shfl_xor_sync(gmask, xw[wd], 2) ^ flip;
+    xw[wd] = bf2_add(bf2_mul(xw[wd], c.w[wd]), bf2_mul(other, s.w[wd]));
   }
 }
 
-__global__ void __launch_bounds__(1024)
+// kMaxThreads = 384 covers up to 16 heads with 80 registers per thread at two CTAs per SM; more heads use
+// the 1024-thread form (64 registers).
+template <int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads, kMaxThreads <= 384 ? 2 : 1)
 prologue_fwd_kernel(const PrologueParams p) {
   const int l8 = threadIdx.x & 7;
   const int g = threadIdx.x >> 3;                  // row of the token: (q|k|v, head)
@@ -94,13 +103,20 @@ prologue_fwd_kernel(const PrologueParams p) {
   __nv_bfloat16* out_c = which == 0 ? p.q_c : (which == 1 ? p.k_c : p.v_c);
   const int64_t bh = static_cast<int64_t>(b) * p.H + h;
 
+  float wreg[8], breg[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    wreg[i] = norm ? __ldg(lw + l8 * 8 + i) : 1.f;
+    breg[i] = norm ? __ldg(lb + l8 * 8 + i) : 0.f;
+  }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float pos_sum = 0.f;                              // of this lane's coordinate (y for lanes 0-3, x for 4-7)
   const int n0 = j * p.block;
-  for (int t = 0; t < p.block; ++t) {
-    const int n = n0 + t;
-    const Vec8 raw = *reinterpret_cast<const Vec8*>(
-        p.qkv + ((static_cast<int64_t>(b) * p.N + n) * 3 * p.H + g) * 64 + l8 * 8);
+  const __nv_bfloat16* src0 = p.qkv + ((static_cast<int64_t>(b) * p.N + n0) * 3 * p.H + g) * 64 + l8 * 8;
+  const int64_t tok_stride = static_cast<int64_t>(3) * p.H * 64;
+  auto load = [&](int t) { return *reinterpret_cast<const Vec8*>(src0 + t * tok_stride); };
+  // one token of this row: accumulate the raw block sum, normalise, rotate, store
+  auto token = [&](int n, const Vec8& raw) {
     float x[8];
 #pragma unroll
     for (int wd = 0; wd < 4; ++wd) { x[2 * wd] = bf16_lo(raw.w[wd]); x[2 * wd + 1] = bf16_hi(raw.w[wd]); }
@@ -108,17 +124,36 @@ prologue_fwd_kernel(const PrologueParams p) {
     for (int i = 0; i < 8; ++i) acc[i] += x[i];
     Vec8 o = raw;
     if (which < 2) {
-      if (norm) ln_row(x, lw, lb, l8 * 8, p.eps, gmask);
+      if (norm) {
+        ln_row(x, wreg, breg, p.eps, gmask);
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) o.w[wd] = pack_bf16(x[2 * wd], x[2 * wd + 1]);
+      }
       if (rope) {
         const int64_t pv = p.pos[(static_cast<int64_t>(b) * p.N + n) * 2 + (l8 >> 2)];
         pos_sum += static_cast<float>(pv);
         const int row = min(max(static_cast<int>(pv), 0), p.tab_rows - 1);
-        rope_row(x, p.cos_tab, p.sin_tab, row, l8, gmask);
+        rope_row(o.w, p.cos_tab, p.sin_tab, row, l8, gmask);
       }
-#pragma unroll
-      for (int wd = 0; wd < 4; ++wd) o.w[wd] = pack_bf16(x[2 * wd], x[2 * wd + 1]);
     }
     *reinterpret_cast<Vec8*>(out + (bh * p.N + n) * 64 + l8 * 8) = o;
+  };
+  // The kernel lives on bytes in flight: the loads of the next four tokens are issued before the current
+  // four are processed (their shuffle and rounding chains are long, the loads are independent of them).
+  Vec8 cur[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (i < p.block) cur[i] = load(i);
+  for (int t0 = 0; t0 < p.block; t0 += 4) {
+    Vec8 nxt[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (t0 + 4 + i < p.block) nxt[i] = load(t0 + 4 + i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (t0 + i < p.block) token(n0 + t0 + i, cur[i]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
   }
   // compression branch: mean of the raw rows, then the same norm and the rotary embedding at the block's
   // mean position (float mean, truncated: xpos.view(..).float().mean(dim=2).int())
@@ -126,17 +161,15 @@ prologue_fwd_kernel(const PrologueParams p) {
   float x[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) x[i] = bf16r(acc[i] * inv);
-  if (which < 2) {
-    if (norm) ln_row(x, lw, lb, l8 * 8, p.eps, gmask);
-    if (rope) {
-      const int pc = static_cast<int>(pos_sum / static_cast<float>(p.block));
-      const int row = min(max(pc, 0), p.tab_rows - 1);
-      rope_row(x, p.cos_tab, p.sin_tab, row, l8, gmask);
-    }
-  }
+  if (norm) ln_row(x, wreg, breg, p.eps, gmask);
   Vec8 o;
 #pragma unroll
   for (int wd = 0; wd < 4; ++wd) o.w[wd] = pack_bf16(x[2 * wd], x[2 * wd + 1]);
+  if (rope) {
+    const int pc = static_cast<int>(pos_sum / static_cast<float>(p.block));
+    const int row = min(max(pc, 0), p.tab_rows - 1);
+    rope_row(o.w, p.cos_tab, p.sin_tab, row, l8, gmask);
+  }
   *reinterpret_cast<Vec8*>(out_c + (bh * p.Nc + j) * 64 + l8 * 8) = o;
 }
 
@@ -180,7 +213,10 @@ extern "C" int s3r_qkv_prologue_fwd(const void* qkv, const int64_t* pos, const v
   p.q_c = static_cast<__nv_bfloat16*>(q_c); p.k_c = static_cast<__nv_bfloat16*>(k_c);
   p.v_c = static_cast<__nv_bfloat16*>(v_c);
   p.B = B; p.H = H; p.N = N; p.Nc = Nc; p.block = block;
-  prologue_fwd_kernel<<<static_cast<unsigned>(grid), 3 * H * 8, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (3 * H * 8 <= 384)
+    prologue_fwd_kernel<384><<<static_cast<unsigned>(grid), 3 * H * 8, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    prologue_fwd_kernel<1024><<<static_cast<unsigned>(grid), 3 * H * 8, 0, static_cast<cudaStream_t>(stream)>>>(p);
   S3R_CUDA(cudaGetLastError());
   return 0;
 }
