@@ -271,6 +271,28 @@ def layer_norm_heads(x, weight, bias, eps=1e-5):
     return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), bias.float(), eps)
 
 
+def qkv_prologue(qkv: torch.Tensor, num_heads: int, block: int = 16, xpos: Optional[torch.Tensor] = None,
+                 q_norm=None, k_norm=None, rope_base: float = 100.0):
+    """The steps between the qkv projection and the two attention calls (sparse_attention.py:95-123)
+    as one function: ``qkv [B,T,3*H*d]`` -> ``(q, k, v [B,H,T,d], q_c, k_c, v_c [B,H,T/block,d])``.
+    ``q_norm``/``k_norm`` are ``(weight, bias)`` pairs or None; the pooled q and k get the same norm and
+    the rotary embedding at the truncated mean position of their block."""
+    B, T, _ = qkv.shape
+    H = num_heads
+    d = qkv.shape[-1] // (3 * H)
+    q_c, k_c, v_c = pool_qkv(qkv, H, block, block)
+    full = qkv.reshape(B, T, 3, H, d).transpose(1, 3)
+    q, k, v = full[:, :, 0], full[:, :, 1], full[:, :, 2]
+    if q_norm is not None:
+        q_c, q = (layer_norm_heads(t, q_norm[0], q_norm[1]).to(v.dtype) for t in (q_c, q))
+        k_c, k = (layer_norm_heads(t, k_norm[0], k_norm[1]).to(v.dtype) for t in (k_c, k))
+    if xpos is not None:
+        pc = block_positions(xpos, block)
+        q_c, k_c = rope2d(q_c, pc, rope_base), rope2d(k_c, pc, rope_base)
+        q, k = rope2d(q, xpos, rope_base), rope2d(k, xpos, rope_base)
+    return q, k, v, q_c, k_c, v_c
+
+
 def module_forward(params: dict, x: torch.Tensor, xpos: Optional[torch.Tensor], num_heads: int,
                    block_size: int = 4, topk: int = 32, rope_base: float = 100.0,
                    return_aux: bool = False, idx_override: Optional[torch.Tensor] = None):

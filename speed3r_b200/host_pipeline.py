@@ -29,6 +29,18 @@ from . import ops
 _ROWS_PER_CTA = 256          # pooled query rows one compression-attention CTA owns
 
 
+def rows_per_chunk_for(num_heads: int, sm_count: int) -> int:
+    """Pooled query rows per chunk such that one compression-attention launch (``num_heads *
+    ceil(rows/256)`` CTAs, one CTA per SM at a time) fills whole waves of the GPU."""
+    return _ROWS_PER_CTA * (sm_count // math.gcd(num_heads, sm_count))
+
+
+def query_chunks(num_pooled_rows: int, rows_per_chunk: int):
+    """[(first pooled row, last pooled row + 1)] covering ``num_pooled_rows`` in order; the last may be short."""
+    rows = max(1, min(num_pooled_rows, rows_per_chunk))
+    return [(r, min(num_pooled_rows, r + rows)) for r in range(0, num_pooled_rows, rows)]
+
+
 def _pinned(t: Tensor, name: str) -> None:
     if t.device.type != "cpu" or not t.is_pinned():
         raise RuntimeError(f"{name}: expected a pinned host tensor")
@@ -56,7 +68,7 @@ class HostPipeline:
         self.Nc = T // block_size
         if rows_per_chunk is None:
             sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
-            rows_per_chunk = _ROWS_PER_CTA * (sms // math.gcd(H, sms))
+            rows_per_chunk = rows_per_chunk_for(H, sms)
         self.rows = max(1, min(self.Nc, rows_per_chunk))
         self.heads_per_copy = max(1, min(H, heads_per_copy))
         bf = dict(device=self.dev, dtype=torch.bfloat16)
@@ -71,7 +83,7 @@ class HostPipeline:
 
     def chunks(self):
         """[(first pooled row, last pooled row + 1)] of the query chunks."""
-        return [(r, min(self.Nc, r + self.rows)) for r in range(0, self.Nc, self.rows)]
+        return query_chunks(self.Nc, self.rows)
 
     @torch.no_grad()
     def __call__(self, hq: Tensor, hk: Tensor, hv: Tensor, hgate: Tensor, hy: Tensor) -> None:

@@ -106,3 +106,15 @@ def test_rope_matches_oracle_on_cpu():
     assert torch.equal(speed3r_b200.RoPE2D(100.0)(x, pos), R.rope2d(x, pos, 100.0))
     xb = x.bfloat16()
     assert torch.equal(speed3r_b200.RoPE2D(100.0)(xb, pos), R.rope2d(xb, pos, 100.0))
+
+
+def test_host_pipeline_chunking():
+    """Query chunks of the pinned-host pipeline: whole waves of the compression kernel, full cover, in order."""
+    from speed3r_b200.host_pipeline import query_chunks, rows_per_chunk_for
+    rows = rows_per_chunk_for(16, 148)
+    assert rows == 256 * 37 and (16 * (rows // 256)) % 148 == 0
+    assert rows_per_chunk_for(12, 148) == 256 * 37 and rows_per_chunk_for(37, 148) == 256 * 4
+    ch = query_chunks(63000, rows)
+    assert ch[0] == (0, rows) and ch[-1][1] == 63000 and len(ch) == 7
+    assert all(a[1] == b[0] for a, b in zip(ch, ch[1:]))
+    assert query_chunks(100, rows) == [(0, 100)]

@@ -418,6 +418,27 @@ def test_qkv_prologue_matches_separate_steps(with_norm, with_pos, H, Bs):
         assert_bf16_close(a, b.float(), name, max_abs=4e-2, mean_abs=1e-3)
 
 
+def test_qkv_prologue_against_oracle():
+    """The prologue kernel against the fp32 CPU restatement on the module fixture's projection (bf16-rounded):
+    bf16 rounding of LayerNorm and of the three rotary roundings is the only difference."""
+    import speed3r_b200
+    from speed3r_b200 import ops
+    g = golden("module_fwd")
+    sd = {k[len("param."):]: v for k, v in g.items() if k.startswith("param.")}
+    heads = int(g["heads"])
+    qkv, = bf16_round(torch.nn.functional.linear(g["x"], sd["qkv.weight"], sd["qkv.bias"]))
+    ref = R.qkv_prologue(qkv, heads, 16, g["xpos"], (sd["q_norm.weight"], sd["q_norm.bias"]),
+                         (sd["k_norm.weight"], sd["k_norm.bias"]))
+    rope = speed3r_b200.RoPE2D(100.0)
+    xpos = g["xpos"].to(DEV)
+    cos, sin = rope._cos_sin(32, rope._seq_len(xpos), torch.device(DEV), torch.bfloat16)
+    out = ops.qkv_prologue(dev(qkv), heads, 16, xpos, cos, sin,
+                           (sd["q_norm.weight"], sd["q_norm.bias"], 1e-5), (sd["k_norm.weight"], sd["k_norm.bias"], 1e-5))
+    for name, a, b in zip(("q", "k", "v", "q_c", "k_c", "v_c"), out, ref):
+        # the rotary angles are rounded to bf16 before cos/sin on both sides; values reach ~4
+        assert_bf16_close(a, b, "prologue " + name, max_abs=6e-2, mean_abs=6e-3)
+
+
 def test_module_forward_without_grad_uses_fused_prologue_and_matches():
     """Under no_grad the module runs the one-pass prologue; its output equals the grad-enabled path's up to
     bf16 rounding, and agrees with the oracle as the other path does."""

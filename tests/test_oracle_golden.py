@@ -135,3 +135,18 @@ def test_baseline_config1_op():
     torch.testing.assert_close(lse_s, g["lse_s"], **FP)
     y = R.gated_merge(gate, o_c, o_s, Bs)
     torch.testing.assert_close(y[:, ::8], g["y_sub"], **FP)
+
+
+def test_prologue_restatement_is_the_module_prologue():
+    """`qkv_prologue` is the same arithmetic `module_forward` (pinned to the reference's module output above)
+    runs inline: identical tensors on the module fixture."""
+    import torch.nn.functional as F
+    g = golden("module_fwd")
+    sd = {k[len("param."):]: v for k, v in g.items() if k.startswith("param.")}
+    heads = int(g["heads"])
+    _, aux = R.module_forward(sd, g["x"], g["xpos"], heads, return_aux=True)
+    qkv = F.linear(g["x"], sd["qkv.weight"], sd["qkv.bias"])
+    out = R.qkv_prologue(qkv, heads, 16, g["xpos"], (sd["q_norm.weight"], sd["q_norm.bias"]),
+                         (sd["k_norm.weight"], sd["k_norm.bias"]))
+    for name, t in zip(("q", "k", "v", "q_c", "k_c", "v_c"), out):
+        assert torch.equal(t, aux[name]), name
