@@ -15,9 +15,10 @@
 // to the second MMA straight from tensor memory.  S of a tile may be overwritten by the next
 // Q K^T only after both its softmax and its top-k warpgroup have read it.
 //
-// Online softmax with a lazily updated maximum: the exponent offset only moves when the running
-// maximum grows by more than 2^8, and only then is O rescaled in tensor memory, by the softmax
-// threads themselves (each owns one TMEM lane).
+// Online softmax with a lazily updated offset: the exponent offset starts at the first tile's row
+// maximum and only moves when a tile's sum of P shows that the scores have outgrown it by ~2^24; only
+// then is O rescaled in tensor memory, by the softmax threads themselves (each owns one TMEM lane).
+// No per-score maximum is tracked in between.
 //
 // Top-k.  Per row, shared memory holds the best 32 entries (key(score), ~column) as a binary min-heap
 // whose root is the worst kept entry; the row's threshold is the root's score.  Everything is done by
@@ -294,11 +295,10 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const bool tail = (col0 + 128 > p.Nc);
 
       // One pass with tensor-memory loads kept one chunk ahead of the arithmetic: P is computed
-      // with the exponent offset carried over from earlier tiles while the tile's maximum is
-      // gathered on the side.  Only if some row's maximum outgrew its offset by more than 2^8 is
-      // the tile redone with the new offset (O and l rescaled).  S stays valid until this
-      // warpgroup arrives on p_full, so the redo re-reads it.  Tile 0 has no offset yet: its
-      // maximum is taken first.
+      // with the exponent offset carried over from earlier tiles.  Only if some row's scores have
+      // outgrown its offset so far that P nears overflow is the tile redone with the row's exact
+      // maximum as the new offset (O and l rescaled).  S stays valid until this warpgroup arrives
+      // on p_full, so the redo re-reads it.  Tile 0 has no offset yet: its maximum is taken first.
       auto mask_tail = [&](uint32_t (&x)[16], int c8) {
         const int nvalid = min(16, max(0, p.Nc - (col0 + c8 * 16)));
 #pragma unroll
@@ -319,17 +319,15 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         m_used = rmax0 * cs;
       }
       float ls[4];
-      bool redo;
+      bool redo, redone = false;
       do {
         ls[0] = ls[1] = ls[2] = ls[3] = 0.f;
-        float rm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         auto process = [&](uint32_t (&x)[16], int c8) {
           if (tail) mask_tail(x, c8);
           uint32_t pk[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float s0 = __uint_as_float(x[2 * i]), s1 = __uint_as_float(x[2 * i + 1]);
-            rm[i & 3] = fmax3(rm[i & 3], s0, s1);
             const float p0 = fast_exp2(fmaf(s0, cs, -m_used));
             const float p1 = fast_exp2(fmaf(s1, cs, -m_used));
             ls[i & 3] += p0 + p1;
@@ -348,12 +346,29 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (c8 + 2 < 8) tmem_ld16(t_s + (c8 + 2) * 16, xa);
           process(xb, c8 + 1);
         }
-        const float mt = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3])) * cs;
-        const bool need = mt > m_used + 8.f;
-        redo = __any_sync(0xffffffffu, need);
+        // The offset m_used may lag behind the row's true maximum: P is then large, which costs nothing
+        // (bf16 and fp32 keep their relative precision, O and l are fp32) until it nears overflow.  The tile's
+        // own sum of P tells: every P is positive, so max P <= sum <= 128 max P, and no per-score maximum has
+        // to be tracked.  Past 2^24 (or on a non-finite sum) the tile is redone once with the exact maximum.
+        const float tsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        const bool need = !(tsum <= 16777216.f);
+        redo = !redone && __any_sync(0xffffffffu, need);
         if (redo) {
-          const float factor = need ? fast_exp2(m_used - mt) : 1.f;
-          if (need) {
+          redone = true;
+          float rmax = -INFINITY;
+#pragma unroll 1
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint32_t x[16];
+            tmem_ld16(t_s + c8 * 16, x);
+            tmem_ld_wait();
+            if (tail) mask_tail(x, c8);
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) rmax = fmax3(rmax, __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+          }
+          const float mt = rmax * cs;
+          const bool grow = need && mt > m_used;
+          const float factor = grow ? fast_exp2(m_used - mt) : 1.f;
+          if (grow) {
             m_used = mt;
             l *= factor;
           }
@@ -430,6 +445,17 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (i >= nvalid) x[i] = 0xff7fffffu;   // -FLT_MAX: never a hit, and 0 * it stays finite
+        }
+        // Once the lists have filled, most chunks hold no hit for any of the warp's 32 rows: a
+        // three-input max tree (8 instructions for 16 scores) and one vote skip the mask below for them.
+        {
+          const float m0 = fmax3(__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]));
+          const float m1 = fmax3(__uint_as_float(x[3]), __uint_as_float(x[4]), __uint_as_float(x[5]));
+          const float m2 = fmax3(__uint_as_float(x[6]), __uint_as_float(x[7]), __uint_as_float(x[8]));
+          const float m3 = fmax3(__uint_as_float(x[9]), __uint_as_float(x[10]), __uint_as_float(x[11]));
+          const float m4 = fmax3(__uint_as_float(x[12]), __uint_as_float(x[13]), __uint_as_float(x[14]));
+          const float cm = fmaxf(fmax3(fmax3(m0, m1, m2), m3, m4), __uint_as_float(x[15]));
+          if (!__any_sync(0xffffffffu, cm > thr)) return;
         }
         // Hit mask on the FMA pipe (compares, selects and logic ops all share the half-rate ALU
         // pipe, which this kernel saturates first):  t = saturate((x - thr) * 2^60) is 1.0 for a

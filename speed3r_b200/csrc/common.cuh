@@ -127,16 +127,34 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when the phase did not complete within the limit (of the order
-// of a second) or when another thread of the CTA has already given up (*abort_flag != 0); the
-// caller then unwinds instead of spinning for ever.
+// Probe that lets the hardware park the thread for up to `hint_ns` while the phase is pending: a parked
+// warp issues nothing, whereas a spinning one competes for issue slots with the warps doing the work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the phase did not complete within about a second or when another
+// thread of the CTA has already given up (*abort_flag != 0); the caller then unwinds instead of
+// spinning for ever.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > 2048) {
-      __nanosleep(64);
-      if (*abort_flag) return false;
-    }
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > 1000000000ull) break;
   }
   *abort_flag = 1u;
   return false;
