@@ -125,28 +125,33 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const bool producer = active && (wig == 0) && (lane == 0);
 
   const bool chunked = p.Tc != p.Tk;
+  // Called by the whole first warp of the group: lane 0 arms the barrier, then lanes 0..2*nb-1 issue one TMA
+  // tiled copy each (even lanes a key block, odd lanes its value block), so the copies of a stage cost the
+  // warp one instruction stream instead of 2*nb in a row.
   auto issue = [&](int it) {
     const int s = it % C::kStages;
     const int blk0 = it * C::kBlkPerStage;
     const int nb = min(C::kBlkPerStage, nvalid - blk0);
     uint64_t* bar = &ctl.full[group][s];
-    mbar_expect_tx(bar, static_cast<uint32_t>(nb * BS * 128 * 2));
-    uint8_t* kdst = grp_ptr + s * C::kStageBytes;
-    uint8_t* vdst = kdst + C::kStageKeys * 128;
-    for (int j = 0; j < nb; ++j) {
+    if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(nb * BS * 128 * 2));
+    __syncwarp();
+    if (lane < 2 * nb) {
+      const int j = lane >> 1;
+      const bool values = (lane & 1) != 0;
       const int t0 = ctl.list[group][blk0 + j] * BS;
       int ch = 0, tl = t0;
       if (chunked) { ch = t0 / p.Tc; tl = t0 - ch * p.Tc; }
-      tma_load_4d(kdst + j * BS * 128, &map_k, bar, 0, tl, bh, ch);
-      tma_load_4d(vdst + j * BS * 128, &map_v, bar, 0, tl, bh, ch);
+      uint8_t* dst = grp_ptr + s * C::kStageBytes + (values ? C::kStageKeys * 128 : 0) + j * BS * 128;
+      tma_load_4d(dst, values ? &map_v : &map_k, bar, 0, tl, bh, ch);
     }
   };
 
   if (producer) {
     mbar_expect_tx(&ctl.qbar[group], C::kQBytes);
     tma_load_4d(grp_ptr + C::kStages * C::kStageBytes, &map_q, &ctl.qbar[group], 0, qb * BS, bh, 0);
-    for (int it = 0; it < min(C::kStages, nstages); ++it) issue(it);
   }
+  if (active && wig == 0)
+    for (int it = 0; it < min(C::kStages, nstages); ++it) issue(it);
 
   // ---- per-warp state -----------------------------------------------------------------------
   constexpr int NT = C::kStageKeys / 8;          // S n-tiles per stage
@@ -289,11 +294,10 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // release the stage; the group's producer refills it once every warp of the group is done
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl.empty[group][s]);
-      if (producer && it + C::kStages < nstages) {
-        if (!mbar_wait(&ctl.empty[group][s], ph, abort_flag)) { ok = false; }
+      if (wig == 0 && it + C::kStages < nstages) {
+        if (!mbar_wait_warp(&ctl.empty[group][s], ph, abort_flag)) ok = false;
         else issue(it + C::kStages);
       }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
     }
   }
