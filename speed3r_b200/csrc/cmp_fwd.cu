@@ -448,20 +448,21 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         // Once the lists have filled, most chunks hold no hit for any of the warp's 32 rows: a
         // three-input max tree (8 instructions for 16 scores) and one vote skip the mask below for them.
+        float cm;
         {
           const float m0 = fmax3(__uint_as_float(x[0]), __uint_as_float(x[1]), __uint_as_float(x[2]));
           const float m1 = fmax3(__uint_as_float(x[3]), __uint_as_float(x[4]), __uint_as_float(x[5]));
           const float m2 = fmax3(__uint_as_float(x[6]), __uint_as_float(x[7]), __uint_as_float(x[8]));
           const float m3 = fmax3(__uint_as_float(x[9]), __uint_as_float(x[10]), __uint_as_float(x[11]));
           const float m4 = fmax3(__uint_as_float(x[12]), __uint_as_float(x[13]), __uint_as_float(x[14]));
-          const float cm = fmaxf(fmax3(fmax3(m0, m1, m2), m3, m4), __uint_as_float(x[15]));
+          cm = fmaxf(fmax3(fmax3(m0, m1, m2), m3, m4), __uint_as_float(x[15]));
           if (!__any_sync(0xffffffffu, cm > thr)) return;
         }
         // Hit mask on the FMA pipe (compares, selects and logic ops all share the half-rate ALU
         // pipe, which this kernel saturates first):  t = saturate((x - thr) * 2^60) is 1.0 for a
         // hit and 0.0 otherwise (the fused product is exact before rounding, so any x > thr gives
-        // >= 1);  sum t * 2^i is the mask, sum t * x the value of the hit when there is exactly
-        // one.  Chunks with several hits, or a full buffer, take the indexed path below, which
+        // >= 1);  sum t * 2^i is the mask; when there is exactly one hit it is the chunk's maximum,
+        // which the tree above has left in cm.  Chunks with several hits, or a full buffer, take the indexed path below, which
         // appends in ascending column order (that is what keeps equal scores in column order).
         // (2^90: exact for thresholds below 2^37 in magnitude and score gaps above 2^-90, i.e. for
         // every pair of distinct fp32 logits larger than 2^-66 in magnitude.)
@@ -469,7 +470,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // while the list has free slots (thr = -inf) every real score is a hit, the -FLT_MAX fillers
         // of the tail are not: a large finite offset does both (an infinite one would not)
         const float nthr = (thr == -INFINITY) ? 3.0e38f : -thr * kHuge;
-        float acc0 = 0.f, acc1 = 0.f, hv0 = 0.f, hv1 = 0.f;
+        float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float a = __uint_as_float(x[i]), b = __uint_as_float(x[8 + i]);
@@ -477,12 +478,10 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const float t1 = __saturatef(fmaf(b, kHuge, nthr));
           acc0 = fmaf(t0, static_cast<float>(1u << i), acc0);
           acc1 = fmaf(t1, static_cast<float>(256u << i), acc1);
-          hv0 = fmaf(t0, a, hv0);
-          hv1 = fmaf(t1, b, hv1);
         }
         uint32_t m = __float2uint_rn(acc0 + acc1);
-        const float hv = hv0 + hv1;
-        // (a zero or non-finite sum goes the indexed way: the sum cannot tell -0.0 from +0.0)
+        const float hv = cm;
+        // (a zero or non-finite maximum goes the indexed way: max cannot tell -0.0 from +0.0)
         if (m != 0u && (m & (m - 1u)) == 0u && cnt < kPend && hv != 0.f && fabsf(hv) < INFINITY) {
           my_pend[cnt * 32] = make_uint2(sortable_key(hv), static_cast<uint32_t>(cbase + __ffs(m) - 1));
           ++cnt;
