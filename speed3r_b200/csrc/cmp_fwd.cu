@@ -256,16 +256,24 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             ok = mbar_wait(&ctl.p_full[t], j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            // The next scores are what the 256 waiting threads need; P V only has to finish before the next
+            // P V of the tile.  So when the top-k warps have released S already, Q K^T goes first.
+            const bool qk_first = nxt && mbar_test_wait(&ctl.tk_done[t], j & 1);
+            if (qk_first) {
+              tc_fence_after();
+              issue_qk(t, sn);
+              umma_commit(&ctl.s_full[t]);
+            }
             issue_pv(t, s, j > 0);
             if (t == 1) umma_commit(&ctl.v_empty[s]);
-            if (nxt) {
+            if (nxt && !qk_first) {
               ok = mbar_wait(&ctl.tk_done[t], j & 1, abort_flag);    // S of this tile has been read by top-k too
               if (!ok) break;
               tc_fence_after();
               issue_qk(t, sn);
               umma_commit(&ctl.s_full[t]);
-              if (t == 1) umma_commit(&ctl.k_empty[sn]);
             }
+            if (nxt && t == 1) umma_commit(&ctl.k_empty[sn]);
           }
         }
       }
@@ -479,15 +487,20 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           acc0 = fmaf(t0, static_cast<float>(1u << i), acc0);
           acc1 = fmaf(t1, static_cast<float>(256u << i), acc1);
         }
-        uint32_t m = __float2uint_rn(acc0 + acc1);
-        const float hv = cm;
+        // The mask is an exact integer below 2^16 held in a float: a single hit is a power of two (zero
+        // mantissa) whose exponent is the column.  Read off the bits, this keeps the float-to-int
+        // conversion and the find-first-set (both on the pipe the exponentials keep busy) out of the common case.
+        const float accf = acc0 + acc1;
+        const uint32_t ab = __float_as_uint(accf);
+        bool left = accf != 0.f;
         // (a zero or non-finite maximum goes the indexed way: max cannot tell -0.0 from +0.0)
-        if (m != 0u && (m & (m - 1u)) == 0u && cnt < kPend && hv != 0.f && fabsf(hv) < INFINITY) {
-          my_pend[cnt * 32] = make_uint2(sortable_key(hv), static_cast<uint32_t>(cbase + __ffs(m) - 1));
+        if (left && (ab & 0x7fffffu) == 0u && cnt < kPend && cm != 0.f && fabsf(cm) < INFINITY) {
+          my_pend[cnt * 32] = make_uint2(sortable_key(cm), static_cast<uint32_t>(cbase) + (ab >> 23) - 127u);
           ++cnt;
-          m = 0u;
+          left = false;
         }
-        if (!__any_sync(0xffffffffu, m != 0u)) return;             // nothing left anywhere in the warp
+        if (!__any_sync(0xffffffffu, left)) return;                // nothing left anywhere in the warp
+        uint32_t m = left ? __float2uint_rn(accf) : 0u;
         if (m) {
           // this thread's own copy of the chunk, so that a hit can be fetched by its (dynamic) index
           uint4* s4 = reinterpret_cast<uint4*>(scratch);
