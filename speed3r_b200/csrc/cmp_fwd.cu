@@ -465,6 +465,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const float m4 = fmax3(__uint_as_float(x[12]), __uint_as_float(x[13]), __uint_as_float(x[14]));
           cm = fmaxf(fmax3(fmax3(m0, m1, m2), m3, m4), __uint_as_float(x[15]));
           if (!__any_sync(0xffffffffu, cm > thr)) return;
+          if (p.flags & 4) return;                 // profiling: prefilter only (idx is then meaningless)
         }
         // Hit mask on the FMA pipe (compares, selects and logic ops all share the half-rate ALU
         // pipe, which this kernel saturates first):  t = saturate((x - thr) * 2^60) is 1.0 for a
@@ -570,7 +571,8 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 using namespace s3r;
 
-// Profiling switch: bit 1 set = skip the top-k scan (idx is then meaningless).  0 by default.
+// Profiling switch: bit 1 set = skip the top-k scan, bit 2 set = stop after its prefilter (idx is then
+// meaningless).  0 by default.
 static int g_cmp_variant = 0;
 extern "C" void s3r_debug_set_cmp_variant(int v) { g_cmp_variant = v; }
 
