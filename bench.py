@@ -345,9 +345,9 @@ def main():
             kern["sel_frac_hbm"] = kern["sel_dram_gbs"] / peaks["hbm_gbs"]
         ach = f_cmp / t_cmp / 1e9
         # DRAM traffic of one launch, measured with ncu on this very workload (1000 views, one pass:
-        # dram__bytes_read.sum 394.0 MB + dram__bytes_write.sum 235.7 MB, profiles/cmp_fwd_kernel_1000views_dram.md);
+        # dram__bytes_read.sum 392.4 MB + dram__bytes_write.sum 235.1 MB, profiles/cmp_fwd_kernel_1000views_dram.md);
         # it equals the algorithmic bytes (inputs read once, outputs written once) and grows with views.
-        traffic = 629.7e6 * (args.views / 1000.0)
+        traffic = 627.5e6 * (args.views / 1000.0)
         roof = {"kernel": "cmp_fwd_kernel (compression attention + top-k)", "bound": "tensor", "achieved": ach,
                 "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": traffic,
                 "traffic_unit": "bytes/launch (ncu dram read+write measured at 1000 views, scaled by views)",
