@@ -338,14 +338,14 @@ def main():
                 "cmp_tflops": f_cmp / t_cmp / 1e9, "sel_gather_gbs": sel_bytes / t_sel / 1e6,
                 "sel_tflops": f_sel / t_sel / 1e9}
         # the gather figure counts every selected block as if it came from DRAM; L2 serves part of it.  DRAM
-        # traffic of this kernel measured with ncu on this workload (profiles/sel_fwd_kernel_1000views_dram.md):
+        # traffic of this kernel measured with ncu on this workload (one-pass capture of one launch):
         # 64.21 GB read + 2.07 GB written per launch at 1000 views (not proportional to views: L2 hit rate changes)
         if args.views == 1000:
             kern["sel_dram_gbs"] = 66.27e9 / t_sel / 1e6
             kern["sel_frac_hbm"] = kern["sel_dram_gbs"] / peaks["hbm_gbs"]
         ach = f_cmp / t_cmp / 1e9
         # DRAM traffic of one launch, measured with ncu on this very workload (1000 views, one pass:
-        # dram__bytes_read.sum 392.4 MB + dram__bytes_write.sum 235.1 MB, profiles/cmp_fwd_kernel_1000views_dram.md);
+        # dram__bytes_read.sum 392.4 MB + dram__bytes_write.sum 235.1 MB);
         # it equals the algorithmic bytes (inputs read once, outputs written once) and grows with views.
         traffic = 627.5e6 * (args.views / 1000.0)
         roof = {"kernel": "cmp_fwd_kernel (compression attention + top-k)", "bound": "tensor", "achieved": ach,
