@@ -109,8 +109,8 @@ int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, voi
                           int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
                           void* stream);
 
-/* Profiling switch of the kernel above: 0 (default) = normal; 2 = skip the top-k scan, which
- * leaves idx meaningless and exists only to time the attention part alone. */
+/* Profiling switch of the kernel above: 0 (default) = normal; 2 = skip the top-k scan; 4 = stop the
+ * scan after its prefilter.  Both leave idx meaningless and exist only to time parts of the kernel. */
 void s3r_debug_set_cmp_variant(int variant);
 
 /* Backward of the compression attention.  Replaces FlashAttnTopkFunc.backward /

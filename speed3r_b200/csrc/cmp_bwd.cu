@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(kCbWarps * 32) cmp_bwd_dq_kernel(const CmpBwdP
   store_acc_bf16(dq, [&](int r) { return (wrow0 + r < p.Nq) ? out + r * 64 : nullptr; }, lane);
 }
 
-__global__ void __launch_bounds__(kCbWarps * 32) cmp_bwd_dkdv_kernel(const CmpBwdParams p) {
+__global__ void __launch_bounds__(kCbWarps * 32, 2) cmp_bwd_dkdv_kernel(const CmpBwdParams p) {
   __shared__ __align__(16) uint8_t smem[2][kCbStageBytes];
   __shared__ float stats[2][2 * kCbTile];      // [stage][lse2 x64 | delta x64]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
