@@ -220,6 +220,7 @@ def main():
         raise SystemExit("fwdbwd is single-GPU in this benchmark")
     dy = torch.randn(1, Tl, H * D, device=dev, generator=g).bfloat16() if bwd else None
     side = torch.cuda.Stream() if world > 1 else None
+    side_group = dist.new_group(list(range(world))) if world > 1 else None     # own communicator for the large all-gather
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     marks = []
@@ -241,7 +242,7 @@ def main():
             return r
 
         y, _ = seq_parallel.sparse_attention_partitioned(q_, k_, v_, g_, BS, TOPK, ops.pool_tokens, cmp_fn, sel_fn,
-                                                         side_stream=side)
+                                                         side_stream=side, side_group=side_group)
         if record:
             marks.append(e)
         return y

@@ -50,7 +50,7 @@ def chunks_to_dense(xc: Tensor) -> Tensor:
 
 def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, block: int, topk: int,
                                  pool: Callable, cmp_attn_topk: Callable, sel_attn_merge: Callable,
-                                 group=None, side_stream: Optional["torch.cuda.Stream"] = None):
+                                 group=None, side_stream: Optional["torch.cuda.Stream"] = None, side_group=None):
     """Local shard of the op.  ``q,k,v [B,H,T/G,d]`` and ``gate [B,H,T/G,2]`` are this rank's tokens.
 
     ``pool(x, kernel, stride)``; ``cmp_attn_topk(q_c, k_c, v_c, topk) -> (o_c, idx)``;
@@ -58,16 +58,24 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
     the chunked ``[G,B,H,T/G,d]`` layout.  Returns ``(y_local, idx_local)``.
 
     With ``side_stream`` the token-level all-gather (the large one) runs on that stream while
-    the compression attention, which only needs pooled data, runs on the current stream.
+    the compression attention, which only needs pooled data, runs on the current stream.  With a
+    ``side_group`` as well (a second process group over the same ranks, i.e. its own communicator)
+    the large all-gather is issued first and the pooled ones run beside it instead of ahead of it.
     """
+    k_all = v_all = None
+    cur = torch.cuda.current_stream() if side_stream is not None else None
+    if side_stream is not None and side_group is not None:
+        side_stream.wait_stream(cur)              # k and v are ready on the current stream
+        with torch.cuda.stream(side_stream):
+            k_all, v_all = all_gather_chunks(k, side_group), all_gather_chunks(v, side_group)
     q_c, k_c, v_c = pool(q, block, block), pool(k, block, block), pool(v, block, block)
     kc_all = chunks_to_dense(all_gather_chunks(k_c, group))
     vc_all = chunks_to_dense(all_gather_chunks(v_c, group))
     if side_stream is not None:
-        cur = torch.cuda.current_stream()
-        side_stream.wait_stream(cur)
-        with torch.cuda.stream(side_stream):
-            k_all, v_all = all_gather_chunks(k, group), all_gather_chunks(v, group)
+        if k_all is None:
+            side_stream.wait_stream(cur)
+            with torch.cuda.stream(side_stream):
+                k_all, v_all = all_gather_chunks(k, group), all_gather_chunks(v, group)
         o_c, idx = cmp_attn_topk(q_c, kc_all, vc_all, topk)
         cur.wait_stream(side_stream)
         k_all.record_stream(cur)
