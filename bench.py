@@ -219,7 +219,8 @@ def main():
     if bwd and world > 1:
         raise SystemExit("fwdbwd is single-GPU in this benchmark")
     dy = torch.randn(1, Tl, H * D, device=dev, generator=g).bfloat16() if bwd else None
-    side = torch.cuda.Stream() if world > 1 else None
+    # high priority: the all-gather's few CTAs must not queue behind the compression kernel, which fills every SM
+    side = torch.cuda.Stream(priority=-1) if world > 1 else None
     side_group = dist.new_group(list(range(world))) if world > 1 else None     # own communicator for the large all-gather
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
