@@ -12,6 +12,13 @@ T = views*1008; gate = sigmoid(N(0,1)).  The metric is effective sparse TFLOP/s
 
 N > 1 (launched with torch.distributed.run): the sequence is partitioned by query blocks over the
 ranks; pooled and token-level K/V are all-gathered (NCCL).  Total work is fixed -> strong scaling.
+Every rank draws the GLOBAL tensors from one seed and keeps its slice, so that (outside the timed
+region) each rank can run the single-GPU op on the global tensors and check that its shard of the
+partitioned result is bit-identical (`parity` in the JSON line).
+
+At N = 1 the line also carries `triton_baseline`: the reference's own Triton kernels (unmodified, from
+baseline/_ref, installed by baseline/install_ref.sh) timed on the same GPU and the same tensors, and
+the dense `F.scaled_dot_product_attention` time at the same sequence length.
 
 --impl reference times the CPU restatement of the reference's algorithm (the reference itself is
 Python + Triton and is not present on the benchmark machine) on a bounded sample of the same
@@ -165,7 +172,7 @@ def run_reference_arm(args):
 def workload_config(args):
     T = args.views * TOK_PER_VIEW
     return {"workload": f"sparse global-attention op, {args.mode}, {args.views} views x {TOK_PER_VIEW} tokens "
-                        f"(T={T}), H={H}, d={D}, pool {BS}/{BS}, select block {BS}, top-{TOPK}",
+                        f"(T={T}), H={H}, d={D}, pool {BS}/{BS}, select block {BS}, top-{TOPK}, {getattr(args, 'inputs', 'iid')} inputs",
             "tokens": T, "views": args.views, "mode": args.mode,
             "parallelism": f"sp{args.gpus}" if args.gpus > 1 else "single",
             "l2": "inputs (q,k,v: 3 x %.1f GB) larger than the 126 MB L2" % (T * H * D * 2 / 1e9)}
@@ -174,6 +181,103 @@ def workload_config(args):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+def make_inputs(args, T, dev):
+    """q, k, v [1,H,T,64] bf16 after a per-head LayerNorm and gate [1,H,T,2], from ONE seed (the same
+    tensors on every rank).  `structured`: every token's key/query is the sum of a component shared by
+    its view, a component shared by its patch position across views and noise, mixed through a rank-16
+    map, so that neighbouring query blocks select overlapping key blocks (as real multi-view features do)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(1234)
+    ln = lambda t: torch.nn.functional.layer_norm(t, (D,))
+    if args.inputs == "iid":
+        q, k, v = (ln(torch.randn(1, H, T, D, device=dev, generator=g)).bfloat16() for _ in range(3))
+    else:
+        views, tok = T // TOK_PER_VIEW, TOK_PER_VIEW
+        def structured():
+            r = 16
+            view = torch.randn(1, H, views, 1, r, device=dev, generator=g)
+            patch = torch.randn(1, H, 1, tok, r, device=dev, generator=g)
+            mix = torch.randn(1, H, r, D, device=dev, generator=g) / 4.0
+            low = ((view + patch).reshape(1, H, T, r) @ mix)
+            return ln(low + 0.5 * torch.randn(1, H, T, D, device=dev, generator=g)).bfloat16()
+        q, k = structured(), structured()
+        v = ln(torch.randn(1, H, T, D, device=dev, generator=g)).bfloat16()
+    gate = torch.sigmoid(torch.randn(1, H, T, 2, device=dev, generator=g)).bfloat16()
+    return q, k, v, gate
+
+
+def triton_baseline(q, k, v, views):
+    """The reference's own kernels (flash_attention_topk.forward_with_topk :156-200 and
+    topk_blocksparse_attention._topk_blocksparse_attention_fwd :852-904) from baseline/_ref, unmodified,
+    on the same device and tensors: pooled q,k,v -> compression attention + top-k -> selection attention.
+    Returns a dict for the JSON line (`unavailable` with the reason when it cannot run)."""
+    import torch
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "pi3")):
+        return {"unavailable": "baseline/_ref is empty (run baseline/install_ref.sh where the reference checkout is)"}
+    try:
+        if ref not in sys.path:
+            sys.path.insert(0, ref)
+        import triton
+        from pi3.models.sparse_attn.flash_attention_topk import forward_with_topk
+        from pi3.models.sparse_attn.topk_blocksparse_attention import _topk_blocksparse_attention_fwd
+        from speed3r_b200 import ops
+        qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (q, k, v))
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+
+        def timed(fn, warm, reps):
+            for i in range(warm):
+                try:
+                    fn()
+                except RuntimeError:
+                    if i > 0:            # the first JIT of a kernel can fail on a helper reference and pass on retry
+                        raise
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            a.record()
+            for _ in range(reps):
+                out = fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps, out
+
+        warm = 10
+        t_cmp, (o_c, _, idx, _) = timed(lambda: forward_with_topk(qc, kc, vc, TOPK), warm, 3)
+        t_sel, (o_s, _) = timed(lambda: _topk_blocksparse_attention_fwd(q, k, v, idx, BS, 1.0 / math.sqrt(D)), warm, 3)
+        o2, idx2 = ops.flash_attn_topk_func(qc, kc, vc, TOPK)
+        o3 = ops.topk_blocksparse_attention(q, k, v, idx, BS)
+        torch.cuda.synchronize()
+        return {"what": "reference Triton kernels, unmodified: forward_with_topk + _topk_blocksparse_attention_fwd "
+                        "(pooling by this library; the merge is not included)",
+                "triton": triton.__version__, "views": views, "warmup": warm, "reps": 3,
+                "cmp_attn_topk_ms": t_cmp, "sel_attn_ms": t_sel, "total_ms": t_cmp + t_sel,
+                "idx_mismatch_fraction_vs_ours": (idx != idx2).float().mean().item(),
+                "o_c_max_abs_diff_vs_ours": (o_c.float() - o2.float()).abs().max().item(),
+                "o_s_max_abs_diff_vs_ours": (o_s.float() - o3.float()).abs().max().item()}
+    except Exception as e:      # Triton failing to compile or run these kernels on this GPU is a result, not a crash
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
+
+
+def dense_baseline(q, k, v):
+    """Dense attention over the same sequence with the library flash kernel (F.scaled_dot_product_attention)."""
+    import torch
+    try:
+        f = lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v)
+        f()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        f()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        T = q.shape[2]
+        return {"what": "F.scaled_dot_product_attention, same q,k,v, 1 iteration after 1 warm-up", "ms": ms,
+                "tflops": 4.0 * T * T * D * H / ms / 1e9}
+    except Exception as e:
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +289,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--module", action="store_true", help="also time the whole attention module at this size")
+    ap.add_argument("--inputs", default="iid", choices=["iid", "structured"],
+                    help="iid: q,k,v ~ N(0,1) per token; structured: keys/queries = low-rank view + patch components")
+    ap.add_argument("--no-triton-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 5:
@@ -211,10 +319,12 @@ def main():
     T = args.views * TOK_PER_VIEW
     t0, t1 = seq_parallel.partition(T, BS, world, rank)
     Tl = t1 - t0
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    ln = lambda t: torch.nn.functional.layer_norm(t, (D,))
-    q, k, v = (ln(torch.randn(1, H, Tl, D, device=dev, generator=g)).bfloat16() for _ in range(3))
-    gate = torch.sigmoid(torch.randn(1, H, Tl, 2, device=dev, generator=g)).bfloat16()
+    qg, kg, vg, gateg = make_inputs(args, T, dev)           # GLOBAL tensors, identical on every rank
+    if world > 1:
+        q, k, v, gate = (t[:, :, t0:t1].contiguous() for t in (qg, kg, vg, gateg))
+    else:
+        q, k, v, gate = qg, kg, vg, gateg
+    g = torch.Generator(device=dev).manual_seed(99)
     bwd = args.mode == "fwdbwd"
     if bwd and world > 1:
         raise SystemExit("fwdbwd is single-GPU in this benchmark")
@@ -226,7 +336,7 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)
     marks = []
 
-    def step_partitioned(q_, k_, v_, g_, record=False):
+    def step_partitioned(q_, k_, v_, g_, record=False, with_idx=False):
         """N > 1: this rank's query blocks; events around the two attention kernels when recording."""
         e = [ev() for _ in range(4)] if record else None
 
@@ -242,11 +352,11 @@ def main():
             if record: e[3].record()
             return r
 
-        y, _ = seq_parallel.sparse_attention_partitioned(q_, k_, v_, g_, BS, TOPK, ops.pool_tokens, cmp_fn, sel_fn,
-                                                         side_stream=side, side_group=side_group)
+        y, idx_ = seq_parallel.sparse_attention_partitioned(q_, k_, v_, g_, BS, TOPK, ops.pool_tokens, cmp_fn, sel_fn,
+                                                            side_stream=side, side_group=side_group)
         if record:
             marks.append(e)
-        return y
+        return (y, idx_) if with_idx else y
 
     def step(record=False):
         """Returns y; with record=True also appends per-kernel CUDA events."""
@@ -313,6 +423,33 @@ def main():
     if status != 0:
         raise SystemExit(f"device status word {status}: a kernel gave up a bounded wait")
 
+    # N > 1, outside the timed region: this rank's shard of the partitioned result against the single-GPU
+    # op run here on the global tensors.  The chunked-K/V kernel is bit-identical to the dense one, so
+    # equality is the bar, for the output and for the selected-block table.
+    parity = None
+    if world > 1 and not bwd and not args.no_parity:
+        with torch.no_grad():
+            y_sh, idx_sh = step_partitioned(q, k, v, gate, with_idx=True)
+            qc_, kc_, vc_ = (ops.pool_tokens(t, BS, BS) for t in (qg, kg, vg))
+            o_c_, idx_f = ops.flash_attn_topk_func(qc_, kc_, vc_, TOPK)
+            y_f = ops.sel_attn_merge(qg, kg, vg, idx_f, gateg, o_c_, BS)
+            ok_y = torch.equal(y_sh, y_f[:, t0:t1])
+            ok_i = torch.equal(idx_sh, idx_f[:, :, t0 // BS:t1 // BS])
+            flags = torch.tensor([1.0 if ok_y else 0.0, 1.0 if ok_i else 0.0], device=dev)
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            del y_sh, idx_sh, qc_, kc_, vc_, o_c_, idx_f, y_f
+        parity = {"ok": bool(flags[0].item() == 1.0 and flags[1].item() == 1.0),
+                  "y_bit_equal": bool(flags[0].item() == 1.0), "idx_bit_equal": bool(flags[1].item() == 1.0),
+                  "checked": f"on every one of the {world} ranks: y and idx shards of the partitioned op == the same "
+                             f"rows of the single-GPU op on the global tensors ({args.views} views)"}
+    tri = dense = None
+    if world == 1 and not bwd and not args.no_triton_baseline:
+        with torch.no_grad():
+            tri = triton_baseline(q, k, v, args.views)
+            dense = dense_baseline(q, k, v)
+        torch.cuda.empty_cache()
+    del qg, kg, vg, gateg
+
     f_cmp, f_sel = flops_fwd(T)
     ftot = (f_cmp + f_sel) * (3.5 if bwd else 1.0)
     value = ftot / (ms * 1e-3) / 1e12
@@ -326,7 +463,10 @@ def main():
         t_cmp, t_sel = avg(0), avg(2)
         ach = f_cmp / world / t_cmp / 1e9
         kern = {"cmp_attn_topk_ms": t_cmp, "sel_attn_merge_ms": t_sel, "rank": 0,
-                "cmp_tflops_per_gpu": ach, "sel_tflops_per_gpu": f_sel / world / t_sel / 1e9}
+                "cmp_tflops_per_gpu": ach, "sel_tflops_per_gpu": f_sel / world / t_sel / 1e9,
+                # what of the step is not the two attention kernels on rank 0: pooling, the pooled all-gathers
+                # the compression kernel waits for, and the part of the token K/V all-gather it does not cover
+                "exposed_comm_ms": ms - t_cmp - t_sel}
         roof = {"kernel": "cmp_fwd_kernel (compression attention + top-k), rank 0", "bound": "tensor", "achieved": ach,
                 "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": None,
                 "peak_source": f"{peaks['src']} sustained bf16 (kernel timed inside a long step)"}
@@ -459,6 +599,16 @@ def main():
                     roofline=roof, kernels=kern, cpu_baseline=cpu)
         if module is not None:
             line["module"] = module
+        if parity is not None:
+            line["parity"] = parity
+        if tri is not None:
+            line["triton_baseline"] = tri
+            if "total_ms" in tri and kern is not None:
+                line["triton_baseline"]["speedup_of_ours"] = tri["total_ms"] / (kern["cmp_attn_topk_ms"] + kern["sel_attn_merge_ms"])
+        if dense is not None:
+            line["dense_baseline"] = dense
+            if "ms" in dense:
+                line["dense_baseline"]["fraction_of_dense_time"] = ms / dense["ms"]
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -35,7 +35,7 @@ extern "C" {
 #define S3R_ERR_TOO_LARGE (-6)   /* exceeds the capacity of a fixed-size buffer */
 
 #define S3R_STATUS_WAIT_TIMEOUT 1u /* a bounded device-side wait gave up */
-#define S3R_STATUS_BAD_INDEX 2u    /* an index-table entry was out of range and was skipped */
+#define S3R_STATUS_BAD_INDEX 2u    /* s3r_qkv_prologue_fwd met a position outside its cos/sin tables (row clamped) */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int s3r_version(void);
@@ -79,7 +79,8 @@ int s3r_pool_bwd(const void* d_out, void* d_in, int64_t stride_b, int64_t stride
  *   qkv            : [B,N,3,H,d] bf16, contiguous (the output of the qkv Linear)
  *   pos            : [B,N,2] int64 (y,x) or NULL (no rotary embedding)
  *   cos_tab/sin_tab: [tab_rows, d/2] bf16, row p = cos/sin of bf16(p * inv_freq) duplicated over the two
- *                    halves (what RoPE2D caches); positions are clamped to the table
+ *                    halves (what RoPE2D caches); a position outside the table is clamped and
+ *                    raises S3R_STATUS_BAD_INDEX in the device status word
  *   q_weight..k_bias: fp32 [d] LayerNorm affine parameters, or all NULL (Identity norms)
  *   q,k,v          : [B,H,N,d] bf16 out;  q_c,k_c,v_c : [B,H,N/block,d] bf16 out
  * N must be a multiple of `block`; d = 64; at most 42 heads.  Forward only: a caller that
@@ -103,15 +104,12 @@ int s3r_qkv_prologue_fwd(const void* qkv, const int64_t* pos, const void* cos_ta
  *         Nc < topk the tail holds Nc-1, as the reference's zero-initialised running set does.
  *   Rows [q_row0, q_row0+Nq) of a longer query sequence can be processed against all Nc keys
  *   by passing q_c/o_c/lse/idx pointers of that slice (sequence-partitioned use).
- *   topk <= 32.  The running top-k sets live in shared memory; the call needs no scratch.
+ *   topk <= 32.  The running top-k sets live in shared memory; the call needs no scratch and keeps no
+ *   state between calls.
  * ------------------------------------------------------------------------------------------ */
 int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
                           int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
                           void* stream);
-
-/* Profiling switch of the kernel above: 0 (default) = normal; 2 = skip the top-k scan; 4 = stop the
- * scan after its prefilter.  Both leave idx meaningless and exist only to time parts of the kernel. */
-void s3r_debug_set_cmp_variant(int variant);
 
 /* Backward of the compression attention.  Replaces FlashAttnTopkFunc.backward /
  * _flash_attn_backward and its three kernels (flash_attention_topk.py:204-630).  No gradient
@@ -212,19 +210,6 @@ int s3r_sel_attn_bwd(const void* q, const void* k, const void* v, const int32_t*
                      const int32_t* qids, const float* lse_s, const float* delta_s, const void* do_s,
                      void* dq, void* dk, void* dv, int B, int H, int Tq, int Tk, int d, int block, int topk,
                      float scale, void* stream);
-
-/* ------------------------------------------------------------------------------------------
- * Plain SIMT restatements of the two forward attentions, one thread per query row, fp32
- * arithmetic.  They exist so that the tensor-core kernels can be cross-checked ON THE DEVICE
- * at sizes a CPU check cannot reach; nothing in the product path calls them.
- * Same arguments and semantics as s3r_cmp_attn_topk_fwd / s3r_sel_attn_fwd (o_s, lse_s only).
- * ------------------------------------------------------------------------------------------ */
-int s3r_check_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
-                                int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
-                                void* stream);
-int s3r_check_sel_attn_fwd(const void* q, const void* k, const void* v, const int32_t* idx, void* o_s,
-                           float* lse_s, int B, int H, int Tq, int Tk, int d, int block, int topk, float scale,
-                           void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,7 +23,6 @@ SIGNATURES = {
     "s3r_pool_bwd": (_i, [_p, _p, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p]),
     "s3r_qkv_prologue_fwd": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "s3r_cmp_attn_topk_fwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
-    "s3r_debug_set_cmp_variant": (None, [_i]),
     "s3r_cmp_attn_bwd": (_i, [_p] * 10 + [_i, _i, _i, _i, _i, _f, _p]),
     "s3r_sel_attn_fwd": (_i, [_p, _p, _p, _i, _i64, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p,
                               _i, _i, _i, _i, _i, _i, _i, _f, _p]),
@@ -33,12 +32,21 @@ SIGNATURES = {
     "s3r_merge_bwd": (_i, [_p, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "s3r_delta": (_i, [_p, _p, _p, _i64, _i, _p]),
     "s3r_sel_attn_bwd": (_i, [_p] * 12 + [_i, _i, _i, _i, _i, _i, _i, _f, _p]),
+}
+
+# the tests-only companion library (include/speed3r_b200_check.h); nothing in the package calls it
+CHECK_LIB_PATH = os.path.join(_PKG, "libspeed3r_b200_check.so")
+CHECK_SIGNATURES = {
     "s3r_check_cmp_attn_topk_fwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
     "s3r_check_sel_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p]),
+    "s3r_check_wait_gives_up": (_i, [C.c_uint64, _p, _p]),
+    "s3r_last_error": (_i, [C.c_char_p, _i]),
+    "s3r_device_status": (_i, [C.POINTER(C.c_uint32), _i]),
 }
 
 _lock = threading.Lock()
 _lib = None
+_check_lib = None
 
 
 def load() -> C.CDLL:
@@ -57,6 +65,23 @@ def load() -> C.CDLL:
             fn.argtypes = args
         _lib = lib
         return lib
+
+
+def load_check() -> C.CDLL:
+    """The tests-only companion library (device-side cross-checks, the bounded-wait probe)."""
+    global _check_lib
+    with _lock:
+        if _check_lib is None:
+            if not os.path.exists(CHECK_LIB_PATH):
+                from . import build as _build
+                _build.build()
+            lib = C.CDLL(CHECK_LIB_PATH)
+            for name, (res, args) in CHECK_SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype = res
+                fn.argtypes = args
+            _check_lib = lib
+        return _check_lib
 
 
 def last_error() -> str:

@@ -1,5 +1,7 @@
 """Build recipe for the C-ABI library: every ``csrc/*.cu`` is compiled for sm_100a with nvcc and
-linked into ``speed3r_b200/libspeed3r_b200.so`` (kept in-tree, next to the package).
+linked into ``speed3r_b200/libspeed3r_b200.so`` (kept in-tree, next to the package).  The tests-only
+companion ``libspeed3r_b200_check.so`` (``csrc/check/*.cu`` plus the shared host plumbing) is built
+beside it; the package never loads it.
 
     python -m speed3r_b200.build [-v] [--force]
 """
@@ -16,6 +18,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "csrc", "build")
 LIB = os.path.join(PKG, "libspeed3r_b200.so")
+CHECK_LIB = os.path.join(PKG, "libspeed3r_b200_check.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -43,6 +46,7 @@ def _stale(target: str, deps) -> bool:
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(PKG, "..", "include", "*.h"))
+    os.makedirs(OBJ, exist_ok=True)
     if _stale(obj, [src] + headers):
         cmd = [_nvcc()] + NVCC_FLAGS + ["-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -62,13 +66,17 @@ def build(verbose: bool = False, force: bool = False) -> str:
         for f in glob.glob(os.path.join(OBJ, "*.o")):
             os.remove(f)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile(s, verbose), srcs))
-    if _stale(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    check_srcs = sorted(glob.glob(os.path.join(CSRC, "check", "*.cu")))
+    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) + len(check_srcs))) as ex:
+        all_objs = list(ex.map(lambda s: _compile(s, verbose), srcs + check_srcs))
+    objs, check_objs = all_objs[:len(srcs)], all_objs[len(srcs):]
+    api_obj = [o for o in objs if os.path.basename(o) == "api.o"]
+    for lib, members in ((LIB, objs), (CHECK_LIB, check_objs + api_obj)):
+        if _stale(lib, members):
+            cmd = [_nvcc(), "-shared", "-o", lib] + members + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return LIB
 
 

@@ -1,8 +1,8 @@
 // Plain one-thread-per-query-row restatements of the two forward attentions (fp32 arithmetic on
 // the bf16 inputs, exact expf/logf).  They are slow and exist only so that tests can cross-check
 // the tensor-core kernels on the device at sizes a CPU check cannot reach.  No product path
-// calls them.
-#include "common.cuh"
+// calls them.  The file also holds the probe of the bounded wait (a wait that is made to run out).
+#include "../common.cuh"
 
 namespace s3r {
 
@@ -106,9 +106,39 @@ check_sel_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __res
   LSE[static_cast<int64_t>(bh) * Tq + row] = l > 0.f ? m + logf(l) : -INFINITY;
 }
 
+// One warp waits on a barrier nobody arrives on; the bounded wait has to give up after limit_ns.
+__global__ void wait_probe_kernel(uint64_t limit_ns, uint64_t* waited_ns, uint32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const uint64_t t0 = globaltimer_ns();
+  const bool ok = mbar_wait_warp(&bar, 0, &abort_flag, limit_ns);
+  const uint64_t dt = globaltimer_ns() - t0;
+  if (threadIdx.x == 0) {
+    *waited_ns = dt;
+    if (!ok) atomicOr(status, kStatusWaitTimeout);
+  }
+}
+
 }  // namespace s3r
 
 using namespace s3r;
+
+extern "C" int s3r_check_wait_gives_up(uint64_t limit_ns, uint64_t* waited_ns, void* stream) {
+  S3R_REQUIRE(waited_ns != nullptr, S3R_ERR_NULL, "s3r_check_wait_gives_up: NULL pointer");
+  S3R_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ull, S3R_ERR_UNSUPPORTED,
+              "s3r_check_wait_gives_up: the limit must be within (0, 100 ms]");
+  uint32_t* status = device_status_ptr();
+  S3R_REQUIRE(status != nullptr, S3R_ERR_DRIVER, "s3r_check_wait_gives_up: could not resolve the device status word");
+  wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, waited_ns, status);
+  S3R_CUDA(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int s3r_check_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
                                            int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,

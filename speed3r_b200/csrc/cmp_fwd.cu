@@ -69,7 +69,7 @@ constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 struct CmpCtl {
   uint64_t q_full, o_full;
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-  uint64_t s_full[2], p_full[2], tk_done[2];
+  uint64_t s_full[2], p_full[2], tk_done[2], pv_done[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -78,7 +78,7 @@ struct CmpParams {
   __nv_bfloat16* o;
   float* lse;
   int32_t* idx;
-  int Nq, Nc, topk, flags;
+  int Nq, Nc, topk;
   float c_scale;        // softmax scale * log2(e)
   uint32_t* status;
 };
@@ -181,6 +181,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_init(&ctl.s_full[t], 1);
       mbar_init(&ctl.p_full[t], 128);
       mbar_init(&ctl.tk_done[t], 128);
+      mbar_init(&ctl.pv_done[t], 1);
     }
     mbar_fence_init();
   }
@@ -265,6 +266,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               umma_commit(&ctl.s_full[t]);
             }
             issue_pv(t, s, j > 0);
+            umma_commit(&ctl.pv_done[t]);          // P of this tile may be overwritten, O is at rest
             if (t == 1) umma_commit(&ctl.v_empty[s]);
             if (nxt && !qk_first) {
               ok = mbar_wait(&ctl.tk_done[t], j & 1, abort_flag);    // S of this tile has been read by top-k too
@@ -325,6 +327,13 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int i = 0; i < 16; ++i) rmax0 = fmaxf(rmax0, __uint_as_float(x[i]));
         }
         m_used = rmax0 * cs;
+      }
+      // P of the previous tile must have been consumed by its P V before it is overwritten, and O must be
+      // at rest before a rescale: when the issuer put the next Q K^T ahead of P V, s_full alone does not
+      // say so.  The wait is normally satisfied already.
+      if (j > 0) {
+        if (!mbar_wait_warp(&ctl.pv_done[t], (j - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
       }
       float ls[4];
       bool redo, redone = false;
@@ -435,7 +444,6 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     uint2* my_pend = reinterpret_cast<uint2*>(sptr + kOffPend) + (warp - 12) * (kPend * 32) + lane;   // [i][lane]
     int cnt = 0;
     const int topk = p.topk;
-    const bool skip = (p.flags & 2) != 0;
     float thr = -INFINITY;
     bool ok = true;
 
@@ -446,7 +454,6 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const bool tail = (col0 + 128 > p.Nc);
 
       auto handle = [&](uint32_t (&x)[16], int c8) {
-        if (skip) return;
         const int cbase = col0 + c8 * 16;
         if (tail) {
           const int nvalid = min(16, max(0, p.Nc - cbase));
@@ -465,7 +472,6 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const float m4 = fmax3(__uint_as_float(x[12]), __uint_as_float(x[13]), __uint_as_float(x[14]));
           cm = fmaxf(fmax3(fmax3(m0, m1, m2), m3, m4), __uint_as_float(x[15]));
           if (!__any_sync(0xffffffffu, cm > thr)) return;
-          if (p.flags & 4) return;                 // profiling: prefilter only (idx is then meaningless)
         }
         // Hit mask on the FMA pipe (compares, selects and logic ops all share the half-rate ALU
         // pipe, which this kernel saturates first):  t = saturate((x - thr) * 2^60) is 1.0 for a
@@ -540,9 +546,8 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       // the tile is already released; merge the pending hits every few tiles, or early when some
       // buffer is nearly full
-      const int merge_every = (p.flags >> 8) ? (p.flags >> 8) : kMergeEvery;
-      if (!skip && ((j % merge_every) == merge_every - 1 || j == ntiles - 1 ||
-                    __any_sync(0xffffffffu, cnt >= kPend - S3R_CMP_PEND_SLACK)))
+      if ((j % kMergeEvery) == kMergeEvery - 1 || j == ntiles - 1 ||
+          __any_sync(0xffffffffu, cnt >= kPend - S3R_CMP_PEND_SLACK))
         topk_merge_own(my_list, my_pend, cnt, thr, topk);
       __syncwarp();
     }
@@ -570,11 +575,6 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }  // namespace s3r
 
 using namespace s3r;
-
-// Profiling switch: bit 1 set = skip the top-k scan, bit 2 set = stop after its prefilter (idx is then
-// meaningless).  0 by default.
-static int g_cmp_variant = 0;
-extern "C" void s3r_debug_set_cmp_variant(int v) { g_cmp_variant = v; }
 
 extern "C" int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
                                      int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
@@ -609,18 +609,13 @@ extern "C" int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const voi
   p.o = static_cast<__nv_bfloat16*>(o_c);
   p.lse = lse;
   p.idx = idx;
-  p.Nq = Nq; p.Nc = Nc; p.topk = topk; p.flags = g_cmp_variant;
+  p.Nq = Nq; p.Nc = Nc; p.topk = topk;
   p.c_scale = scale * 1.4426950408889634f;
   p.status = device_status_ptr();
   S3R_REQUIRE(p.status != nullptr, S3R_ERR_DRIVER, "s3r_cmp_attn_topk_fwd: could not resolve the device status word");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool attr_set[64] = {};
-  int dev = 0;
-  S3R_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmpSmemBytes));
-    attr_set[dev] = true;
-  }
+  // per device and idempotent: setting it on every call keeps this entry point free of process-global state
+  S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmpSmemBytes));
   const int64_t grid = static_cast<int64_t>(BH) * ((Nq + 255) / 256);
   S3R_REQUIRE(grid < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_cmp_attn_topk_fwd: grid too large");
   cmp_fwd_kernel<<<static_cast<unsigned>(grid), kCmpThreads, kCmpSmemBytes, st>>>(mq, mk, mv, p);

@@ -48,7 +48,7 @@ int sm_count();
 // device helpers
 // ---------------------------------------------------------------------------------------------
 constexpr uint32_t kStatusWaitTimeout = 1u;   // a bounded mbarrier wait gave up
-constexpr uint32_t kStatusBadIndex    = 2u;   // an index-table entry was outside its range
+constexpr uint32_t kStatusBadIndex    = 2u;   // a rotary position was outside the cos/sin tables
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -145,24 +145,30 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  Returns false when the phase did not complete within about a second or when another
-// thread of the CTA has already given up (*abort_flag != 0); the caller then unwinds instead of
-// spinning for ever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// Bounded wait.  Returns false when the phase did not complete within `limit_ns` (about a second in
+// the kernels) or when another thread of the CTA has already given up (*abort_flag != 0); the caller
+// then unwinds instead of spinning for ever.  (Kept inline on purpose: a call at a site that holds a
+// whole row of scores in registers cannot be register-allocated.)
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   while (true) {
     if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > 1000000000ull) break;
+    if (globaltimer_ns() - t0 > limit_ns) break;
   }
   *abort_flag = 1u;
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, 1000000000ull);
+}
 
 // Same, called by all 32 lanes of a converged warp; the result is warp-uniform.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  const bool ok = mbar_wait(bar, parity, abort_flag);
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint64_t limit_ns = 1000000000ull) {
+  const bool ok = mbar_wait_limit(bar, parity, abort_flag, limit_ns);
   return __all_sync(0xffffffffu, ok);
 }
 

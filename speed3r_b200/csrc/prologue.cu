@@ -28,6 +28,7 @@ struct PrologueParams {
   float eps;
   __nv_bfloat16 *q, *k, *v, *q_c, *k_c, *v_c;
   int B, H, N, Nc, block;
+  uint32_t* status;                  // device status word: a position outside the tables sets kStatusBadIndex
 };
 
 struct alignas(16) Vec8 {
@@ -133,6 +134,7 @@ prologue_fwd_kernel(const PrologueParams p) {
         const int64_t pv = p.pos[(static_cast<int64_t>(b) * p.N + n) * 2 + (l8 >> 2)];
         pos_sum += static_cast<float>(pv);
         const int row = min(max(static_cast<int>(pv), 0), p.tab_rows - 1);
+        if (pv != row) atomicOr(p.status, kStatusBadIndex);      // clamped: the result for this token is wrong
         rope_row(o.w, p.cos_tab, p.sin_tab, row, l8, gmask);
       }
     }
@@ -168,6 +170,7 @@ prologue_fwd_kernel(const PrologueParams p) {
   if (rope) {
     const int pc = static_cast<int>(pos_sum / static_cast<float>(p.block));
     const int row = min(max(pc, 0), p.tab_rows - 1);
+    if (pc != row) atomicOr(p.status, kStatusBadIndex);
     rope_row(o.w, p.cos_tab, p.sin_tab, row, l8, gmask);
   }
   *reinterpret_cast<Vec8*>(out_c + (bh * p.Nc + j) * 64 + l8 * 8) = o;
@@ -213,6 +216,8 @@ extern "C" int s3r_qkv_prologue_fwd(const void* qkv, const int64_t* pos, const v
   p.q_c = static_cast<__nv_bfloat16*>(q_c); p.k_c = static_cast<__nv_bfloat16*>(k_c);
   p.v_c = static_cast<__nv_bfloat16*>(v_c);
   p.B = B; p.H = H; p.N = N; p.Nc = Nc; p.block = block;
+  p.status = device_status_ptr();
+  S3R_REQUIRE(p.status != nullptr, S3R_ERR_DRIVER, "s3r_qkv_prologue_fwd: could not resolve the device status word");
   if (3 * H * 8 <= 384)
     prologue_fwd_kernel<384><<<static_cast<unsigned>(grid), 3 * H * 8, 0, static_cast<cudaStream_t>(stream)>>>(p);
   else

@@ -82,10 +82,19 @@ __global__ void csr_fill_kernel(const int32_t* __restrict__ idx, int32_t* __rest
   }
 }
 
-// One warp per (b,h,key block): rank-sort the segment (ascending query block) from tmp into qids.
-__global__ void __launch_bounds__(256) csr_sort_kernel(const int32_t* __restrict__ offsets,
-                                                       const int32_t* __restrict__ tmp, int32_t* __restrict__ qids,
-                                                       int64_t per_bh, int Nkb, int64_t nseg) {
+// The fill above leaves every segment complete but in arrival order; the gradient kernel needs ascending
+// query blocks (a fixed summation order).  Segments are sorted by length class:
+//   len <= 32      one warp ranks the segment with shuffles (the common case: the mean length is top-k)
+//   len <= 4096    one CTA, bitonic network in shared memory
+//   longer         ("sink" key blocks that most query blocks select) one CTA walks the (b,h) slice of the
+//                  table in order and compacts the matching query blocks: O(Nq*topk), no comparison sort
+// The first kernel handles the short class and queues every other segment for the second.
+constexpr int kCsrSmemSort = 4096;
+
+__global__ void __launch_bounds__(256) csr_sort_small_kernel(const int32_t* __restrict__ offsets,
+                                                             const int32_t* __restrict__ tmp, int32_t* __restrict__ qids,
+                                                             int64_t per_bh, int Nkb, int64_t nseg,
+                                                             int32_t* __restrict__ queue) {
   const int lane = threadIdx.x & 31;
   const int64_t seg = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
   if (seg >= nseg) return;
@@ -93,22 +102,95 @@ __global__ void __launch_bounds__(256) csr_sort_kernel(const int32_t* __restrict
   const int n = static_cast<int>(seg - bh * Nkb);
   const int32_t* off = offsets + bh * (Nkb + 1);
   const int beg = off[n], len = off[n + 1] - beg;
-  const int32_t* src = tmp + bh * per_bh + beg;
-  int32_t* dst = qids + bh * per_bh + beg;
-  for (int i0 = 0; i0 < len; i0 += 32) {
-    const int i = i0 + lane;
-    const int32_t x = (i < len) ? src[i] : 0x7fffffff;
-    int rank = 0;
-    for (int j0 = 0; j0 < len; j0 += 32) {
-      const int j = j0 + lane;
-      const int32_t y = (j < len) ? src[j] : 0x7fffffff;
-      const int lim = min(32, len - j0);
-      for (int t = 0; t < lim; ++t) {
-        const int32_t yt = __shfl_sync(0xffffffffu, y, t);
-        rank += (yt < x) || (yt == x && (j0 + t) < i);
+  if (len > 32) {
+    if (lane == 0) queue[1 + atomicAdd(&queue[0], 1)] = static_cast<int32_t>(seg);
+    return;
+  }
+  const int32_t x = (lane < len) ? tmp[bh * per_bh + beg + lane] : 0x7fffffff;
+  int rank = 0;
+  for (int t = 0; t < len; ++t) {
+    const int32_t yt = __shfl_sync(0xffffffffu, x, t);
+    rank += (yt < x) || (yt == x && t < lane);
+  }
+  if (lane < len) qids[bh * per_bh + beg + rank] = x;
+}
+
+__global__ void __launch_bounds__(256) csr_sort_long_kernel(const int32_t* __restrict__ idx,
+                                                            const int32_t* __restrict__ offsets,
+                                                            const int32_t* __restrict__ tmp, int32_t* __restrict__ qids,
+                                                            int64_t per_bh, int Nkb, int topk,
+                                                            const int32_t* __restrict__ queue) {
+  __shared__ int32_t buf[kCsrSmemSort];
+  __shared__ int32_t warp_tot[8];
+  __shared__ int32_t run_base;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nqueued = queue[0];
+  for (int w = blockIdx.x; w < nqueued; w += gridDim.x) {
+    const int64_t seg = queue[1 + w];
+    const int64_t bh = seg / Nkb;
+    const int n = static_cast<int>(seg - bh * Nkb);
+    const int32_t* off = offsets + bh * (Nkb + 1);
+    const int beg = off[n], len = off[n + 1] - beg;
+    int32_t* dst = qids + bh * per_bh + beg;
+    if (len <= kCsrSmemSort) {
+      int P = 64;
+      while (P < len) P <<= 1;
+      const int32_t* src = tmp + bh * per_bh + beg;
+      for (int i = tid; i < P; i += 256) buf[i] = (i < len) ? src[i] : 0x7fffffff;
+      __syncthreads();
+      for (int k = 2; k <= P; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+          for (int i = tid; i < P; i += 256) {
+            const int l = i ^ j;
+            if (l > i) {
+              const int32_t a = buf[i], b = buf[l];
+              const bool up = (i & k) == 0;
+              if ((a > b) == up) { buf[i] = b; buf[l] = a; }
+            }
+          }
+          __syncthreads();
+        }
+      }
+      for (int i = tid; i < len; i += 256) dst[i] = buf[i];
+      __syncthreads();
+    } else {
+      // ordered compaction over the (b,h) slice of the table: 8 consecutive entries per thread
+      const int32_t* tab = idx + bh * per_bh;
+      if (tid == 0) run_base = 0;
+      __syncthreads();
+      for (int64_t base = 0; base < per_bh; base += 256 * 8) {
+        const int64_t i0 = base + static_cast<int64_t>(tid) * 8;
+        int32_t e[8];
+        int cnt = 0;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          e[u] = (i0 + u < per_bh) ? tab[i0 + u] : -1;
+          cnt += (e[u] == n);
+        }
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += y;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        int before = run_base + incl - cnt;
+        int total = 0;
+#pragma unroll
+        for (int ww = 0; ww < 8; ++ww) {
+          const int t = warp_tot[ww];
+          before += (ww < warp) ? t : 0;
+          total += t;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (e[u] == n) dst[before++] = static_cast<int32_t>((i0 + u) / topk);
+        __syncthreads();
+        if (tid == 0) run_base += total;
+        __syncthreads();
       }
     }
-    if (i < len) dst[rank] = x;
   }
 }
 
@@ -400,7 +482,9 @@ extern "C" size_t s3r_csr_workspace_bytes(int B, int H, int Nq, int topk, int Nk
   const size_t bh = static_cast<size_t>(B) * H;
   size_t cursor = (bh * Nkb * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
   size_t tmp = (bh * Nq * topk * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
-  return cursor + tmp;
+  // queue of the segments longer than a warp: at most one per 33 table entries, plus its counter
+  size_t queue = ((bh * Nq * topk / 33 + 2) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
+  return cursor + tmp + queue;
 }
 
 extern "C" int s3r_build_key_csr(const int32_t* idx, int32_t* offsets, int32_t* qids, int B, int H, int Nq, int topk,
@@ -418,12 +502,18 @@ extern "C" int s3r_build_key_csr(const int32_t* idx, int32_t* offsets, int32_t* 
   int32_t* cursor = static_cast<int32_t*>(workspace);
   int32_t* tmp = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) +
                                             ((bh * Nkb * sizeof(int32_t) + 255) & ~static_cast<size_t>(255)));
+  const int64_t nseg = bh * Nkb;
+  S3R_REQUIRE(nseg < (1ll << 31) && total < (1ll << 40), S3R_ERR_TOO_LARGE, "s3r_build_key_csr: table too large");
+  int32_t* queue = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(tmp) +
+                                              ((bh * Nq * topk * sizeof(int32_t) + 255) & ~static_cast<size_t>(255)));
   S3R_CUDA(cudaMemsetAsync(offsets, 0, bh * (Nkb + 1) * sizeof(int32_t), st));
+  S3R_CUDA(cudaMemsetAsync(queue, 0, sizeof(int32_t), st));
   csr_count_kernel<<<grid_for(total, 256), 256, 0, st>>>(idx, offsets, per_bh, total, Nkb);
   csr_scan_kernel<<<static_cast<unsigned>(bh), 1024, 0, st>>>(offsets, cursor, Nkb);
   csr_fill_kernel<<<grid_for(total, 256), 256, 0, st>>>(idx, cursor, tmp, per_bh, total, Nkb, topk);
-  const int64_t nseg = bh * Nkb;
-  csr_sort_kernel<<<static_cast<unsigned>((nseg * 32 + 255) / 256), 256, 0, st>>>(offsets, tmp, qids, per_bh, Nkb, nseg);
+  csr_sort_small_kernel<<<static_cast<unsigned>((nseg * 32 + 255) / 256), 256, 0, st>>>(offsets, tmp, qids, per_bh, Nkb,
+                                                                                        nseg, queue);
+  csr_sort_long_kernel<<<sm_count() * 4, 256, 0, st>>>(idx, offsets, tmp, qids, per_bh, Nkb, topk, queue);
   S3R_CUDA(cudaGetLastError());
   return 0;
 }
@@ -467,8 +557,9 @@ extern "C" int s3r_build_key_csr_static(const int32_t* idx, int32_t* offsets, in
     }
     scratch = dev_ptr[dev];
   }
-  // Nothing in the scratch has to start at zero: the scan writes every cursor and the sort only reads
-  // the slots the fill wrote, so whatever an earlier call left behind is never read.
+  // What must start at zero (the counter of the long-segment queue) is cleared by the build itself; the scan
+  // writes every cursor and the sorts only read slots the fill wrote, so nothing an earlier call left behind
+  // is ever read.
   return s3r_build_key_csr(idx, offsets, qids, B, H, Nq, topk, Nkb, scratch, S3R_CSR_STATIC_SCRATCH_BYTES, stream);
 }
 

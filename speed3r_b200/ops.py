@@ -442,31 +442,3 @@ def sel_attn_merge_chunked(q, k_chunks, v_chunks, topk_idx, gate, o_c, block_siz
         _, _, y = _sel_fwd(q, k_chunks, v_chunks, topk_idx, gate, o_c, int(block_size), float(softmax_scale),
                            False, False, int(k_chunks.shape[0]))
     return y
-
-
-# ------------------------------------------------------------------------------------------------
-# device-side cross-checks (tests only)
-# ------------------------------------------------------------------------------------------------
-def check_cmp_attn_topk(q_c, k_c, v_c, topk, scale=None):
-    B, H, Nq, d = q_c.shape
-    Nc = k_c.shape[2]
-    scale = scale or 1.0 / math.sqrt(d)
-    o = torch.empty_like(q_c)
-    lse = torch.empty(B, H, Nq, device=q_c.device, dtype=torch.float32)
-    idx = torch.empty(B, H, Nq, topk, device=q_c.device, dtype=torch.int32)
-    _lib.check(_lib.load().s3r_check_cmp_attn_topk_fwd(q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), o.data_ptr(),
-                                                       lse.data_ptr(), idx.data_ptr(), B, H, Nq, Nc, d, topk, scale,
-                                                       _stream()), "s3r_check_cmp_attn_topk_fwd")
-    return o, lse, idx
-
-
-def check_sel_attn(q, k, v, idx, block, scale=None):
-    B, H, Tq, d = q.shape
-    Tk = k.shape[2]
-    scale = scale or 1.0 / math.sqrt(d)
-    o = torch.empty_like(q)
-    lse = torch.empty(B, H, Tq, device=q.device, dtype=torch.float32)
-    _lib.check(_lib.load().s3r_check_sel_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), idx.data_ptr(),
-                                                  o.data_ptr(), lse.data_ptr(), B, H, Tq, Tk, d, block,
-                                                  idx.shape[-1], scale, _stream()), "s3r_check_sel_attn_fwd")
-    return o, lse

@@ -15,6 +15,7 @@ defaults.
 """
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -23,18 +24,62 @@ from torch import Tensor, nn
 from . import ops
 
 
+class _TableRows:
+    """How many rows the rotary cos/sin tables need for a position tensor, without reading
+    ``positions.max()`` back on every call.
+
+    Row r of the tables depends on r alone (pos_embed.py:119-129), so a table that is longer than
+    needed gives bit-identical results; only a table that is too SHORT is an error.  The size is
+    therefore grow-only, and the maximum of a position tensor is read back once per tensor
+    *object*: the entry is keyed on the storage-owning base tensor through a weak reference (all
+    the reshaped views the decode loop passes down share one base) together with its in-place
+    version counter, and is dropped when that tensor dies.  A new tensor that happens to reuse
+    the address of an old one is a new object and is measured again."""
+
+    def __init__(self, min_rows: int = 64):
+        self.rows = min_rows
+        self._seen = {}
+
+    def __call__(self, positions: Tensor) -> int:
+        base = positions._base if positions._base is not None else positions
+        key = id(base)
+        hit = self._seen.get(key)
+        if hit is not None and hit[0]() is base and hit[1] == base._version:
+            return self.rows
+        need = int(base.max()) + 1 if base.numel() else 1        # one read-back per position tensor
+        self.rows = max(self.rows, need)
+        seen = self._seen
+        self._seen[key] = (weakref.ref(base, lambda _r, k=key: seen.pop(k, None)), base._version)
+        return self.rows
+
+
+def rope_tables(rope, D: int, rows: int, device, dtype):
+    """cos/sin tables ``[rows, 2*(D/2)]`` with the reference's arithmetic (pos_embed.py:119-129: the
+    angle is rounded to ``dtype`` before cos/sin).  ``rope`` is this package's ``RoPE2D`` or the
+    reference's: for the latter its own ``get_cos_sin`` builds (and caches) the tables."""
+    if hasattr(rope, "_cos_sin"):
+        return rope._cos_sin(D, rows, device, dtype)
+    return rope.get_cos_sin(D, rows, device, dtype)
+
+
+def _is_rope2d(rope) -> bool:
+    """This package's RoPE2D or the reference's pure-PyTorch one (same attributes and table builder)."""
+    return isinstance(rope, RoPE2D) or (hasattr(rope, "base") and hasattr(rope, "F0") and
+                                        callable(getattr(rope, "get_cos_sin", None)))
+
+
 class RoPE2D(nn.Module):
     """2-D rotary embedding with the arithmetic of pi3/models/layers/pos_embed.py:112-159 (the
     angle table is rounded to the activation dtype before cos/sin).  Unlike the reference it does
-    not read ``positions.max()`` back on every call: the table length is cached per position
-    tensor."""
+    not read ``positions.max()`` back on every call: the tables only ever grow, and a position
+    tensor is measured once (see ``_TableRows``)."""
 
     def __init__(self, freq: float = 100.0, F0: float = 1.0):
         super().__init__()
         self.base = freq
         self.F0 = F0
         self._tables = {}
-        self._maxpos = {}
+        self._rows = _TableRows()
 
     def _cos_sin(self, D, seq_len, device, dtype):
         key = (D, seq_len, device, dtype)
@@ -46,13 +91,10 @@ class RoPE2D(nn.Module):
             self._tables[key] = (freqs.cos(), freqs.sin())
         return self._tables[key]
 
+    get_cos_sin = _cos_sin          # the reference's name for the same builder
+
     def _seq_len(self, positions: Tensor) -> int:
-        key = (positions.data_ptr(), tuple(positions.shape), positions._version, positions.device)
-        if key not in self._maxpos:
-            if len(self._maxpos) > 64:
-                self._maxpos.clear()
-            self._maxpos[key] = int(positions.max()) + 1
-        return self._maxpos[key]
+        return self._rows(positions)
 
     @staticmethod
     def _rope1d(tokens, pos1d, cos, sin):
@@ -106,10 +148,12 @@ class SparseFlashAttentionRope(nn.Module):
         self.topk = topk
         self.record_idx = False      # debugging aid: keep the last selected-block table in .last_idx
         self.last_idx = None
+        self._rows = _TableRows()    # table length when the rotary module is the reference's own
 
     def _can_fuse_prologue(self, qkv, x, xpos, N, Bs, d) -> bool:
-        """Inference (nothing to differentiate), norms that are LayerNorm(d) with affine or Identity, the
-        rotary module of this package or none, whole blocks, head counts the kernel takes."""
+        """Inference (nothing to differentiate), norms that are LayerNorm(d) with affine or Identity, a 2-D
+        rotary module (this package's or the reference's pure-PyTorch one) or none, whole blocks, head
+        counts the kernel takes."""
         if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
             return False
         norms = (self.q_norm, self.k_norm)
@@ -118,14 +162,15 @@ class SparseFlashAttentionRope(nn.Module):
                  tuple(m.normalized_shape) == (d,) for m in norms)
         if not (ident or (ln and self.q_norm.eps == self.k_norm.eps)):
             return False
-        if xpos is not None and not isinstance(self.rope, RoPE2D):
+        if xpos is not None and not _is_rope2d(self.rope):
             return False
         return d == 64 and N % Bs == 0 and self.num_heads <= 42
 
     def _forward_fused(self, qkv, gate, xpos, B, N, H, d, Bs) -> Tensor:
         cos = sin = None
         if xpos is not None:
-            cos, sin = self.rope._cos_sin(d // 2, self.rope._seq_len(xpos), qkv.device, qkv.dtype)
+            rows = self.rope._seq_len(xpos) if isinstance(self.rope, RoPE2D) else self._rows(xpos)
+            cos, sin = rope_tables(self.rope, d // 2, rows, qkv.device, qkv.dtype)
         qn = kn = None
         if isinstance(self.q_norm, nn.LayerNorm):
             qn = (self.q_norm.weight, self.q_norm.bias, self.q_norm.eps)

@@ -45,3 +45,44 @@ def assert_idx_match(idx_gpu: torch.Tensor, idx_ref: torch.Tensor, scores: torch
 
 def bf16_round(*ts):
     return [t.to(torch.bfloat16).float() for t in ts]
+
+
+# ------------------------------------------------------------------------------------------------
+# device-side cross-checks: the tests-only companion library (include/speed3r_b200_check.h)
+# ------------------------------------------------------------------------------------------------
+def _check_call(rc, what):
+    import ctypes as C
+    from speed3r_b200 import _lib
+    if rc != 0:
+        buf = C.create_string_buffer(512)
+        _lib.load_check().s3r_last_error(buf, 512)
+        raise RuntimeError(f"{what} failed with code {rc}: {buf.value.decode(errors='replace')}")
+
+
+def check_cmp_attn_topk(q_c, k_c, v_c, topk, scale=None):
+    import math
+    from speed3r_b200 import _lib
+    B, H, Nq, d = q_c.shape
+    Nc = k_c.shape[2]
+    scale = scale or 1.0 / math.sqrt(d)
+    o = torch.empty_like(q_c)
+    lse = torch.empty(B, H, Nq, device=q_c.device, dtype=torch.float32)
+    idx = torch.empty(B, H, Nq, topk, device=q_c.device, dtype=torch.int32)
+    _check_call(_lib.load_check().s3r_check_cmp_attn_topk_fwd(
+        q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), o.data_ptr(), lse.data_ptr(), idx.data_ptr(), B, H, Nq, Nc, d,
+        topk, scale, torch.cuda.current_stream().cuda_stream), "s3r_check_cmp_attn_topk_fwd")
+    return o, lse, idx
+
+
+def check_sel_attn(q, k, v, idx, block, scale=None):
+    import math
+    from speed3r_b200 import _lib
+    B, H, Tq, d = q.shape
+    Tk = k.shape[2]
+    scale = scale or 1.0 / math.sqrt(d)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, Tq, device=q.device, dtype=torch.float32)
+    _check_call(_lib.load_check().s3r_check_sel_attn_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), idx.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, Tq, Tk, d, block,
+        idx.shape[-1], scale, torch.cuda.current_stream().cuda_stream), "s3r_check_sel_attn_fwd")
+    return o, lse

@@ -10,10 +10,11 @@ import torch
 from conftest import ROOT
 
 HEADER = os.path.join(ROOT, "include", "speed3r_b200.h")
+CHECK_HEADER = os.path.join(ROOT, "include", "speed3r_b200_check.h")
 
 
-def declared_functions():
-    src = open(HEADER).read()
+def declared_functions(header=HEADER):
+    src = open(header).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
     return sorted(set(re.findall(r"\b(s3r_[a-z0-9_]+)\s*\(", src)))
 
@@ -21,12 +22,23 @@ def declared_functions():
 def test_header_and_binding_list_agree():
     from speed3r_b200 import _lib
     assert declared_functions() == sorted(_lib.SIGNATURES)
+    assert declared_functions(CHECK_HEADER) == sorted(_lib.CHECK_SIGNATURES)
 
 
 def test_library_exports_every_declared_symbol(lib):
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in the header but missing from the library"
     assert lib.s3r_version() >= 100
+    assert not hasattr(lib, "s3r_check_sel_attn_fwd"), "tests-only kernels must not ship in the product library"
+
+
+def test_check_library_exports_every_declared_symbol():
+    from speed3r_b200 import _lib
+    chk = _lib.load_check()
+    for name in declared_functions(CHECK_HEADER):
+        assert hasattr(chk, name), f"{name} is declared in the check header but missing from the check library"
+    import ctypes
+    assert chk.s3r_check_wait_gives_up(0, None, None) == -4          # argument errors need no GPU
 
 
 def test_argument_errors_are_reported_without_a_gpu(lib):

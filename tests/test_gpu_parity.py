@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from conftest import golden
-from _util import assert_bf16_close, assert_idx_match, bf16_round
+from _util import assert_bf16_close, assert_idx_match, bf16_round, check_cmp_attn_topk, check_sel_attn
 from oracle import restatement as R
 
 pytestmark = pytest.mark.gpu
@@ -60,36 +60,29 @@ def test_pool_packed_qkv_view():
 
 
 # ------------------------------------------------------------------- compression attention + top-k
-def _cmp_case(q, k, v, topk, exact=False, variant=0, what=""):
-    from speed3r_b200 import ops, _lib
+def _cmp_case(q, k, v, topk, exact=False, what=""):
+    from speed3r_b200 import ops
     q, k, v = bf16_round(q, k, v)
     o_ref, lse_ref, idx_ref = R.cmp_attn_topk(q, k, v, topk)
     S = torch.matmul(q, k.transpose(-1, -2))
-    _lib.load().s3r_debug_set_cmp_variant(variant)
-    try:
-        o, lse, idx = ops._cmp_fwd(dev(q), dev(k), dev(v), topk, 1.0 / math.sqrt(q.shape[-1]))
-        torch.cuda.synchronize()
-    finally:
-        _lib.load().s3r_debug_set_cmp_variant(0)
+    o, lse, idx = ops._cmp_fwd(dev(q), dev(k), dev(v), topk, 1.0 / math.sqrt(q.shape[-1]))
+    torch.cuda.synchronize()
     assert_idx_match(idx, idx_ref, S, what + " idx", exact=exact)
     assert_bf16_close(o, o_ref, what + " o_c")
     assert_bf16_close(lse, lse_ref, what + " lse", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
 
 
-@pytest.mark.parametrize("variant", [0])
 @pytest.mark.parametrize("name", ["cmp_basic", "cmp_ragged", "cmp_rect", "cmp_short", "cmp_ties"])
-def test_cmp_attn_topk_golden(name, variant):
+def test_cmp_attn_topk_golden(name):
     g = golden(name)
-    _cmp_case(g["q"], g["k"], g["v"], int(g["topk"]), exact=(name in ("cmp_ties", "cmp_short")), variant=variant,
-              what=f"{name}/v{variant}")
+    _cmp_case(g["q"], g["k"], g["v"], int(g["topk"]), exact=(name in ("cmp_ties", "cmp_short")), what=name)
 
 
-@pytest.mark.parametrize("variant", [0])
 @pytest.mark.parametrize("B,H,Nq,Nc,topk", [(1, 4, 1000, 1000, 32), (2, 2, 300, 2500, 16), (1, 2, 257, 129, 32),
                                             (1, 1, 4032, 4032, 32), (1, 2, 5, 40, 8), (1, 2, 700, 900, 1)])
-def test_cmp_attn_topk_seeded(B, H, Nq, Nc, topk, variant):
+def test_cmp_attn_topk_seeded(B, H, Nq, Nc, topk):
     q, k, v = randn(11, B, H, Nq, 64), randn(12, B, H, Nc, 64), randn(13, B, H, Nc, 64)
-    _cmp_case(q, k, v, topk, variant=variant, what=f"seeded {Nq}x{Nc}/v{variant}")
+    _cmp_case(q, k, v, topk, what=f"seeded {Nq}x{Nc}")
 
 
 def test_cmp_attn_all_equal_scores():
@@ -121,7 +114,7 @@ def test_cmp_attn_matches_device_check_at_scale():
     q, k, v = (torch.nn.functional.layer_norm(torch.randn(B, H, N, 64, device=DEV, generator=g), (64,)).bfloat16()
                for _ in range(3))
     o, lse, idx = ops._cmp_fwd(q, k, v, 32, 0.125)
-    o2, lse2, idx2 = ops.check_cmp_attn_topk(q, k, v, 32, 0.125)
+    o2, lse2, idx2 = check_cmp_attn_topk(q, k, v, 32, 0.125)
     torch.cuda.synchronize()
     assert_bf16_close(o, o2, "o_c vs device check")
     assert_bf16_close(lse, lse2, "lse vs device check", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
@@ -169,7 +162,7 @@ def test_sel_attn_seeded_fwd_bwd(B, H, T, Bs, K):
     qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
     o = ops.topk_blocksparse_attention(qg, kg, vg, idx.to(DEV), Bs)
     assert_bf16_close(o, o_ref, "o_s")
-    o_chk, lse_chk = ops.check_sel_attn(qg.detach(), kg.detach(), vg.detach(), idx.to(DEV), Bs)
+    o_chk, lse_chk = check_sel_attn(qg.detach(), kg.detach(), vg.detach(), idx.to(DEV), Bs)
     assert_bf16_close(o_chk, o_ref, "device check o_s")
     assert_bf16_close(lse_chk, lse_ref, "device check lse", max_abs=5e-3, mean_abs=1e-3, scale_with_ref=False)
     do, = bf16_round(randn(35, B, H, T, 64))
@@ -276,6 +269,34 @@ def test_key_csr_matches_oracle(B, H, Nq, K, Nkb):
         for h in range(H):
             tot = int(offs_ref[b, h, -1])
             assert torch.equal(qids[b, h, :tot].cpu(), qids_ref[b, h, :tot])
+
+
+def test_key_csr_sink_blocks():
+    """Key blocks that (nearly) every query block selects - attention sinks - give segments of thousands
+    of entries: the build must order them as the oracle does (all three length classes of its sort:
+    a warp, a CTA in shared memory, the ordered walk over the table) and do so in milliseconds."""
+    import time
+    from speed3r_b200 import ops
+    B, H, Nq, K, Nkb = 1, 2, 6000, 32, 6000
+    idx = _rand_idx(62, B, H, Nq, Nkb, K - 2)
+    sink = torch.zeros(B, H, Nq, 1, dtype=torch.int32)                         # block 0: listed by everyone (6000)
+    g = torch.Generator().manual_seed(63)
+    mid = torch.where(torch.rand(B, H, Nq, 1, generator=g) < 0.3, 7, -1).int()  # block 7: ~1800 entries (+ random)
+    idx = torch.cat((idx[..., :5], sink, idx[..., 5:], mid), -1).contiguous()
+    offs_ref, qids_ref = R.key_centric_csr(idx, Nkb)
+    assert int(offs_ref[0, 0, 1] - offs_ref[0, 0, 0]) >= Nq and 1000 < int(offs_ref[0, 0, 8] - offs_ref[0, 0, 7]) < 4096
+    idx_d = idx.to(DEV)
+    ops.build_key_csr(idx_d, Nkb)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    offs, qids = ops.build_key_csr(idx_d, Nkb)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert torch.equal(offs.cpu(), offs_ref)
+    for h in range(H):
+        tot = int(offs_ref[0, h, -1])
+        assert torch.equal(qids[0, h, :tot].cpu(), qids_ref[0, h, :tot])
+    assert dt < 0.05, f"index build with sink blocks took {dt * 1e3:.1f} ms"
 
 
 @pytest.mark.parametrize("name", ["cmp_basic", "cmp_ragged"])
@@ -498,6 +519,40 @@ def test_module_under_checkpoint_recompute_is_deterministic():
         y.float().square().mean().backward()
         grads.append(x.grad.clone())
     assert torch.equal(grads[0], grads[1])
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait on a barrier nobody arrives on must end by itself after its limit (1 ms here), return
+    normally and raise the wait-timeout bit of the status word (probe in the tests-only library)."""
+    import ctypes as C
+    from speed3r_b200 import _lib
+    chk = _lib.load_check()
+    word = C.c_uint32(0)
+    assert chk.s3r_device_status(C.byref(word), 1) == 0
+    waited = torch.zeros(1, device=DEV, dtype=torch.int64)
+    rc = chk.s3r_check_wait_gives_up(1_000_000, waited.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert chk.s3r_device_status(C.byref(word), 1) == 0
+    assert word.value & 1, "the wait ended without raising S3R_STATUS_WAIT_TIMEOUT"
+    assert 1_000_000 <= waited.item() < 50_000_000, f"waited {waited.item()} ns for a 1 ms limit"
+    assert chk.s3r_device_status(C.byref(word), 1) == 0 and word.value == 0
+
+
+def test_prologue_flags_positions_outside_its_tables():
+    """A position beyond the cos/sin tables is clamped (no fault) and raises the bad-index status bit."""
+    import speed3r_b200
+    from speed3r_b200 import _lib, ops
+    B, N, H, d, Bs = 1, 64, 2, 64, 16
+    qkv = dev(randn(95, B, N, 3 * H * d))
+    pos = torch.randint(0, 8, (B, N, 2), generator=torch.Generator().manual_seed(96)).to(DEV)
+    cos, sin = speed3r_b200.RoPE2D(100.0)._cos_sin(d // 2, 8, torch.device(DEV), torch.bfloat16)
+    _lib.device_status(clear=True)
+    ops.qkv_prologue(qkv, H, Bs, pos, cos, sin)
+    assert _lib.device_status(clear=True) == 0
+    pos[0, 5, 1] = 11                                  # outside the 8-row tables
+    ops.qkv_prologue(qkv, H, Bs, pos, cos, sin)
+    assert _lib.device_status(clear=True) == 2
 
 
 def test_rejects_cpu_and_fp32():
