@@ -174,7 +174,8 @@ def workload_config(args):
     return {"workload": f"sparse global-attention op, {args.mode}, {args.views} views x {TOK_PER_VIEW} tokens "
                         f"(T={T}), H={H}, d={D}, pool {BS}/{BS}, select block {BS}, top-{TOPK}, {getattr(args, 'inputs', 'iid')} inputs",
             "tokens": T, "views": args.views, "mode": args.mode,
-            "parallelism": f"sp{args.gpus}" if args.gpus > 1 else "single",
+            "parallelism": (f"sp{args.gpus}, token K/V exchange: " + ("copy engines over CUDA IPC" if getattr(args, "gather", "peer") == "peer"
+                                                                       else "NCCL all-gather on a side stream")) if args.gpus > 1 else "single",
             "l2": "inputs (q,k,v: 3 x %.1f GB) larger than the 126 MB L2" % (T * H * D * 2 / 1e9)}
 
 
@@ -278,6 +279,118 @@ def dense_baseline(q, k, v):
         return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
 
 
+def run_model(args):
+    """Forward of the reference's Pi3_Sparse (unmodified code from baseline/_ref, random weights, 392x504
+    images: 28x36 patches = 1008 tokens per view) with the global blocks' attention swapped for this
+    package's class.  With N > 1 every rank holds views/N views: encoder, frame blocks, MLPs and heads
+    are per view and need no communication (pi3/models/pi3_sparse.py:214-321); the global attention runs
+    sequence-partitioned (speed3r_b200.seq_parallel)."""
+    import torch
+    import torch.distributed as dist
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "pi3")):
+        print(json.dumps({"metric": "pi3_sparse_forward_views_per_s", "unavailable":
+                          "baseline/_ref is empty (run baseline/install_ref.sh where the reference checkout is)"}))
+        return
+    sys.path.insert(0, ref)
+    import speed3r_b200
+    from speed3r_b200 import seq_parallel
+    from pi3.models.pi3_sparse import Pi3_Sparse
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.model_attn == "reference" and world > 1:
+        raise SystemExit("the reference attention is single-GPU")
+    if args.views % world:
+        raise SystemExit("--views must be a multiple of --gpus")
+    torch.manual_seed(0)                                   # the same weights on every rank
+    model = Pi3_Sparse()
+    with torch.no_grad():
+        for name, prm in model.named_parameters():         # explicit init: Linear weights trunc-normal(0.02), biases 0,
+            if prm.dim() == 2:                             # the gates keep their (-1,+1) bias
+                torch.nn.init.trunc_normal_(prm, std=0.02)
+            elif prm.dim() == 1 and name.endswith(".bias") and ".gate." not in name:
+                prm.zero_()
+    model = model.to(dev).eval()
+    attns = []
+    if args.model_attn == "ours":
+        sp = seq_parallel.SequenceParallel(gather=args.gather) if world > 1 else None
+        for blk in model.global_decoder:
+            old = blk.attn
+            new = speed3r_b200.SparseFlashAttentionRope(old.qkv.in_features, num_heads=old.num_heads, qkv_bias=True,
+                                                        proj_bias=True, qk_norm=True, rope=model.rope,
+                                                        block_size=old.block_size)
+            new.load_state_dict(old.state_dict())
+            new.seq_parallel = sp
+            blk.attn = new.to(dev)
+    attns = [blk.attn for blk in model.global_decoder]
+    vl = args.views // world
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    imgs = torch.rand(1, vl, 3, 392, 504, device=dev, generator=g)
+    marks = []
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def before(mod, inputs):
+        marks.append([ev(), ev()])
+        marks[-1][0].record()
+
+    def after(mod, inputs, output):
+        marks[-1][1].record()
+
+    for a_ in attns:
+        a_.register_forward_pre_hook(before)
+        a_.register_forward_hook(after)
+
+    def fwd():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            try:
+                return model(imgs)
+            except RuntimeError as e:       # newer Triton than the reference pins: its first launch can fail once
+                if "Unsupported function referenced" not in str(e):
+                    raise
+                return model(imgs)
+
+    warm = max(1, min(args.warmup, 2))
+    for _ in range(warm):
+        fwd()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    marks.clear()
+    steps = max(1, min(args.steps, 3))
+    a, b = ev(), ev()
+    a.record()
+    for _ in range(steps):
+        out = fwd()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    attn_ms = sum(m[0].elapsed_time(m[1]) for m in marks) / steps
+    if world > 1:
+        t = torch.tensor([ms, attn_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, attn_ms = t[0].item(), t[1].item()
+    finite = bool(torch.isfinite(out["points"]).all().item())
+    if rank == 0:
+        print(json.dumps(dict(
+            metric="pi3_sparse_forward_views_per_s", value=args.views / (ms * 1e-3), unit="views/s", n_gpus=world,
+            steps=steps, warmup=warm, ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
+            dtype="bf16", data="synthetic",
+            config={"workload": f"Pi3_Sparse forward (reference model code, random weights), {args.views} views of 392x504, "
+                                f"global attention: {'this library' if args.model_attn == 'ours' else 'reference Triton module'}",
+                    "views": args.views, "tokens": args.views * TOK_PER_VIEW,
+                    "parallelism": f"views sharded over {world} GPUs, global attention sequence-partitioned ({args.gather})"
+                                   if world > 1 else "single"},
+            model={"global_attention_ms": attn_ms, "global_attention_share": attn_ms / ms,
+                   "global_blocks": len(attns), "outputs_finite": finite})))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -291,6 +404,13 @@ def main():
     ap.add_argument("--module", action="store_true", help="also time the whole attention module at this size")
     ap.add_argument("--inputs", default="iid", choices=["iid", "structured"],
                     help="iid: q,k,v ~ N(0,1) per token; structured: keys/queries = low-rank view + patch components")
+    ap.add_argument("--model", action="store_true",
+                    help="time the forward of the reference's own Pi3_Sparse (from baseline/_ref) with this package's "
+                         "attention class swapped in; prints a line of its own (metric pi3_sparse_forward_views_per_s)")
+    ap.add_argument("--model-attn", default="ours", choices=["ours", "reference"],
+                    help="--model: which attention class the global blocks use (reference = its Triton module, 1 GPU only)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: token-level K/V exchange by copy engines over CUDA IPC (peer) or an NCCL all-gather")
     ap.add_argument("--no-triton-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()
@@ -298,6 +418,9 @@ def main():
         if args.steps > 5:
             args.steps = 5
         run_reference_arm(args)
+        return
+    if args.model:
+        run_model(args)
         return
 
     import torch
@@ -317,11 +440,11 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     T = args.views * TOK_PER_VIEW
-    t0, t1 = seq_parallel.partition(T, BS, world, rank)
-    Tl = t1 - t0
+    tok0, tok1 = seq_parallel.partition(T, BS, world, rank)
+    Tl = tok1 - tok0
     qg, kg, vg, gateg = make_inputs(args, T, dev)           # GLOBAL tensors, identical on every rank
     if world > 1:
-        q, k, v, gate = (t[:, :, t0:t1].contiguous() for t in (qg, kg, vg, gateg))
+        q, k, v, gate = (t[:, :, tok0:tok1].contiguous() for t in (qg, kg, vg, gateg))
     else:
         q, k, v, gate = qg, kg, vg, gateg
     g = torch.Generator(device=dev).manual_seed(99)
@@ -332,6 +455,10 @@ def main():
     # high priority: the all-gather's few CTAs must not queue behind the compression kernel, which fills every SM
     side = torch.cuda.Stream(priority=-1) if world > 1 else None
     side_group = dist.new_group(list(range(world))) if world > 1 else None     # own communicator for the large all-gather
+    peer = None
+    if world > 1 and args.gather == "peer":
+        peer = (seq_parallel.PeerGather((1, H, Tl, D), torch.bfloat16, dev),
+                seq_parallel.PeerGather((1, H, Tl, D), torch.bfloat16, dev))
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     marks = []
@@ -353,7 +480,7 @@ def main():
             return r
 
         y, idx_ = seq_parallel.sparse_attention_partitioned(q_, k_, v_, g_, BS, TOPK, ops.pool_tokens, cmp_fn, sel_fn,
-                                                            side_stream=side, side_group=side_group)
+                                                            side_stream=side, side_group=side_group, peer_gather=peer)
         if record:
             marks.append(e)
         return (y, idx_) if with_idx else y
@@ -433,8 +560,8 @@ def main():
             qc_, kc_, vc_ = (ops.pool_tokens(t, BS, BS) for t in (qg, kg, vg))
             o_c_, idx_f = ops.flash_attn_topk_func(qc_, kc_, vc_, TOPK)
             y_f = ops.sel_attn_merge(qg, kg, vg, idx_f, gateg, o_c_, BS)
-            ok_y = torch.equal(y_sh, y_f[:, t0:t1])
-            ok_i = torch.equal(idx_sh, idx_f[:, :, t0 // BS:t1 // BS])
+            ok_y = torch.equal(y_sh, y_f[:, tok0:tok1])
+            ok_i = torch.equal(idx_sh, idx_f[:, :, tok0 // BS:tok1 // BS])
             flags = torch.tensor([1.0 if ok_y else 0.0, 1.0 if ok_i else 0.0], device=dev)
             dist.all_reduce(flags, op=dist.ReduceOp.MIN)
             del y_sh, idx_sh, qc_, kc_, vc_, o_c_, idx_f, y_f

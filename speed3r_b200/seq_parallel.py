@@ -14,6 +14,12 @@ contiguous partition of query blocks is a contiguous partition of views:
 
 The two attention callables are injected so that the host logic can be exercised on CPU ranks
 (gloo) with the oracle standing in for the kernels.
+
+The token-level exchange is the large one (2*T*H*d*2 bytes in total) and is only needed by the
+selection kernel, i.e. after the compression attention.  An NCCL all-gather moves it with CTAs that
+compete with the compression kernel for SMs; ``PeerGather`` moves it with the copy engines instead:
+every rank exposes its shard through CUDA IPC and pulls its peers' shards with plain device-to-device
+copies on side streams while the compression kernel owns every SM.
 """
 from __future__ import annotations
 
@@ -42,6 +48,69 @@ def all_gather_chunks(x: Tensor, group=None) -> Tensor:
     return out.view((world,) + tuple(x.shape))
 
 
+class PeerGather:
+    """All-gather of equally shaped ``[B,H,n,d]`` shards by copy engines (one node, one process per GPU).
+
+    Every rank owns the result buffer ``out [G,B,H,n,d]`` (chunk g = rank g's shard, the layout the
+    selection kernel reads in place) and has mapped its peers' result buffers through CUDA IPC; a rank
+    writes its own shard into ``out[rank]`` and pulls shard g from rank g's ``out[g]``.
+
+    Protocol of one exchange, all calls on the caller's current stream unless said otherwise:
+
+    1. ``stage(x)`` - wait until every rank has finished pulling the previous exchange (a one-element
+       all-reduce: a rank reaches it only after its own pulls), then copy the local shard into
+       ``out[rank]`` (a producer may instead write ``local()`` directly and call ``stage(None)``);
+    2. some collective of the caller that every rank enters AFTER ``stage`` (here: the pooled all-gather)
+       - once it has completed locally, every peer's shard is known to be written;
+    3. ``pull()`` - side streams wait for the current stream, then copy the peers' shards into ``out``
+       (device-to-device copies between GPUs: no SM is used);
+    4. ``wait()`` - the current stream waits for the side streams; ``out`` is complete.
+
+    Peers' memory is only ever the SOURCE of plain copies."""
+
+    def __init__(self, shape, dtype, device, group=None, n_streams: int = 4):
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.shape = tuple(shape)
+        self.out = torch.empty((self.world,) + self.shape, device=device, dtype=dtype)
+        self._token = torch.zeros(1, device=device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, reduce_tensor(self.out), group=group)
+        self.peer_out = [self.out if g == self.rank else rebuild(*args) for g, (rebuild, args) in enumerate(handles)]
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(max(1, min(n_streams, self.world - 1)))]
+        self._done = [torch.cuda.Event() for _ in self.streams]
+        dist.barrier(group=group)                    # every rank has mapped every buffer before first use
+
+    def local(self) -> Tensor:
+        """This rank's slot of the result buffer, ``[B,H,n,d]``."""
+        return self.out[self.rank]
+
+    def stage(self, x: Optional[Tensor]) -> None:
+        dist.all_reduce(self._token, group=self.group)       # nobody is still reading the previous contents
+        if x is not None:
+            self.out[self.rank].copy_(x)
+
+    def pull(self) -> Tensor:
+        cur = torch.cuda.current_stream()
+        for st in self.streams:
+            st.wait_stream(cur)
+        for i in range(1, self.world):                        # the ring after this rank: peers are hit evenly
+            g = (self.rank + i) % self.world
+            with torch.cuda.stream(self.streams[(i - 1) % len(self.streams)]):
+                self.out[g].copy_(self.peer_out[g][g], non_blocking=True)
+        for st, ev in zip(self.streams, self._done):
+            ev.record(st)
+        return self.out
+
+    def wait(self) -> Tensor:
+        cur = torch.cuda.current_stream()
+        for ev in self._done:
+            cur.wait_event(ev)
+        return self.out
+
+
 def chunks_to_dense(xc: Tensor) -> Tensor:
     """``[G,B,H,n,d]`` -> ``[B,H,G*n,d]`` (sequence order restored)."""
     G, B, H, n, d = xc.shape
@@ -50,7 +119,9 @@ def chunks_to_dense(xc: Tensor) -> Tensor:
 
 def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, block: int, topk: int,
                                  pool: Callable, cmp_attn_topk: Callable, sel_attn_merge: Callable,
-                                 group=None, side_stream: Optional["torch.cuda.Stream"] = None, side_group=None):
+                                 group=None, side_stream: Optional["torch.cuda.Stream"] = None, side_group=None,
+                                 peer_gather: Optional[Tuple["PeerGather", "PeerGather"]] = None,
+                                 pooled: Optional[Tuple[Tensor, Tensor, Tensor]] = None):
     """Local shard of the op.  ``q,k,v [B,H,T/G,d]`` and ``gate [B,H,T/G,2]`` are this rank's tokens.
 
     ``pool(x, kernel, stride)``; ``cmp_attn_topk(q_c, k_c, v_c, topk) -> (o_c, idx)``;
@@ -61,14 +132,36 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
     the compression attention, which only needs pooled data, runs on the current stream.  With a
     ``side_group`` as well (a second process group over the same ranks, i.e. its own communicator)
     the large all-gather is issued first and the pooled ones run beside it instead of ahead of it.
+    With ``peer_gather = (PeerGather for k, PeerGather for v)`` the token-level exchange runs on the copy
+    engines instead (see ``PeerGather``); the pooled all-gather is the collective that orders it.
+    ``pooled = (q_c, k_c, v_c)`` of the local tokens skips the pooling (a caller whose prologue has
+    produced them already, with its own normalisation and rotary embedding).
     """
+    def pooled_local():
+        if pooled is not None:
+            return pooled
+        return pool(q, block, block), pool(k, block, block), pool(v, block, block)
+
+    if peer_gather is not None:
+        pk, pv = peer_gather
+        pk.stage(k)
+        pv.stage(v)
+        q_c, k_c, v_c = pooled_local()
+        kc_all = chunks_to_dense(all_gather_chunks(k_c, group))
+        vc_all = chunks_to_dense(all_gather_chunks(v_c, group))
+        pk.pull()
+        pv.pull()
+        o_c, idx = cmp_attn_topk(q_c, kc_all, vc_all, topk)
+        k_all, v_all = pk.wait(), pv.wait()
+        y = sel_attn_merge(q, k_all, v_all, idx, gate, o_c, block)
+        return y, idx
     k_all = v_all = None
     cur = torch.cuda.current_stream() if side_stream is not None else None
     if side_stream is not None and side_group is not None:
         side_stream.wait_stream(cur)              # k and v are ready on the current stream
         with torch.cuda.stream(side_stream):
             k_all, v_all = all_gather_chunks(k, side_group), all_gather_chunks(v, side_group)
-    q_c, k_c, v_c = pool(q, block, block), pool(k, block, block), pool(v, block, block)
+    q_c, k_c, v_c = pooled_local()
     kc_all = chunks_to_dense(all_gather_chunks(k_c, group))
     vc_all = chunks_to_dense(all_gather_chunks(v_c, group))
     if side_stream is not None:
@@ -85,3 +178,35 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
         o_c, idx = cmp_attn_topk(q_c, kc_all, vc_all, topk)
     y = sel_attn_merge(q, k_all, v_all, idx, gate, o_c, block)
     return y, idx
+
+
+class SequenceParallel:
+    """What the drop-in module needs to run its two attention branches sequence-partitioned: set
+    ``module.seq_parallel = SequenceParallel(group)`` on every global-attention module of a model whose
+    ranks each hold a contiguous slice of the views (token order is view-major).  The module's own
+    prologue (split, LayerNorm, rotary embedding, pooling) stays local; this object does the exchange.
+    Forward only (inference)."""
+
+    def __init__(self, group=None, gather: str = "peer"):
+        self.group = group
+        self.gather = gather
+        self._peer = {}
+        self._side = None
+        self._side_group = None
+
+    def attention(self, q: Tensor, k: Tensor, v: Tensor, q_c: Tensor, k_c: Tensor, v_c: Tensor, gate: Tensor,
+                  block: int, topk: int, cmp_attn_topk: Callable, sel_attn_merge: Callable):
+        kw = {}
+        if self.gather == "peer":
+            key = (tuple(k.shape), k.dtype, k.device)
+            if key not in self._peer:
+                self._peer[key] = (PeerGather(k.shape, k.dtype, k.device, self.group),
+                                   PeerGather(k.shape, k.dtype, k.device, self.group))
+            kw["peer_gather"] = self._peer[key]
+        else:
+            if self._side is None:
+                self._side = torch.cuda.Stream(priority=-1)
+                self._side_group = dist.new_group(list(range(dist.get_world_size(self.group))))
+            kw.update(side_stream=self._side, side_group=self._side_group)
+        return sparse_attention_partitioned(q, k, v, gate, block, topk, None, cmp_attn_topk, sel_attn_merge,
+                                            group=self.group, pooled=(q_c, k_c, v_c), **kw)

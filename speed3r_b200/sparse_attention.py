@@ -149,6 +149,7 @@ class SparseFlashAttentionRope(nn.Module):
         self.record_idx = False      # debugging aid: keep the last selected-block table in .last_idx
         self.last_idx = None
         self._rows = _TableRows()    # table length when the rotary module is the reference's own
+        self.seq_parallel = None     # a seq_parallel.SequenceParallel: x holds this rank's slice of the views
 
     def _can_fuse_prologue(self, qkv, x, xpos, N, Bs, d) -> bool:
         """Inference (nothing to differentiate), norms that are LayerNorm(d) with affine or Identity, a 2-D
@@ -176,6 +177,13 @@ class SparseFlashAttentionRope(nn.Module):
             qn = (self.q_norm.weight, self.q_norm.bias, self.q_norm.eps)
             kn = (self.k_norm.weight, self.k_norm.bias, self.k_norm.eps)
         q, k, v, q_c, k_c, v_c = ops.qkv_prologue(qkv.detach(), H, Bs, xpos, cos, sin, qn, kn)
+        if self.seq_parallel is not None:
+            # this rank's query blocks against the whole sequence: pooled and token-level K/V are exchanged
+            y, idx = self.seq_parallel.attention(q, k, v, q_c, k_c, v_c, gate, Bs, self.topk,
+                                                 ops.flash_attn_topk_func, ops.sel_attn_merge_chunked)
+            if self.record_idx:
+                self.last_idx = idx.detach()
+            return self.proj_drop(self.proj(y))
         o_c, idx = ops.flash_attn_topk_func(q_c, k_c, v_c, self.topk)
         if self.record_idx:
             self.last_idx = idx.detach()
@@ -195,6 +203,9 @@ class SparseFlashAttentionRope(nn.Module):
         gate = gate.to(qkv.dtype)
         if self._can_fuse_prologue(qkv, x, xpos, N, Bs, d):
             return self._forward_fused(qkv, gate, xpos, B, N, H, d, Bs)
+        if self.seq_parallel is not None:
+            raise RuntimeError("sequence-parallel attention is inference-only: run under torch.no_grad() with "
+                               "LayerNorm q/k norms, a 2-D rotary module and whole 16-token blocks")
         qkv5 = qkv.view(B, N, 3, H, d)
         q_t, k_t, v_t = (qkv5[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # [B,H,N,d] views of the projection
 

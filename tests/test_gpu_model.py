@@ -220,13 +220,18 @@ def _partition_worker(rank, world, port, views, use_side, result):
         q, k, v = (ln(torch.randn(1, H, T, D, device=dev, generator=g)).bfloat16() for _ in range(3))
         gate = torch.sigmoid(torch.randn(1, H, T, 2, device=dev, generator=g)).bfloat16()
         t0, t1 = seq_parallel.partition(T, BS, world, rank)
-        side = torch.cuda.Stream(priority=-1) if use_side else None
-        side_group = dist.new_group(list(range(world))) if use_side else None
+        side = torch.cuda.Stream(priority=-1) if use_side == "nccl-side" else None
+        side_group = dist.new_group(list(range(world))) if use_side == "nccl-side" else None
+        peer = None
+        if use_side == "peer":
+            shape = (1, H, (t1 - t0), D)
+            peer = (seq_parallel.PeerGather(shape, torch.bfloat16, dev), seq_parallel.PeerGather(shape, torch.bfloat16, dev))
         with torch.no_grad():
             for _ in range(2):                                   # twice: the second call reuses warm communicators
                 y, idx = seq_parallel.sparse_attention_partitioned(
                     *(t[:, :, t0:t1].contiguous() for t in (q, k, v, gate)), BS, K, ops.pool_tokens,
-                    ops.flash_attn_topk_func, ops.sel_attn_merge_chunked, side_stream=side, side_group=side_group)
+                    ops.flash_attn_topk_func, ops.sel_attn_merge_chunked, side_stream=side, side_group=side_group,
+                    peer_gather=peer)
             qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (q, k, v))
             o_c, idx_f = ops.flash_attn_topk_func(qc, kc, vc, K)
             y_f = ops.sel_attn_merge(q, k, v, idx_f, gate, o_c, BS)
@@ -240,10 +245,11 @@ def _partition_worker(rank, world, port, views, use_side, result):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_side", [False, True])
+@pytest.mark.parametrize("use_side", ["nccl", "nccl-side", "peer"])
 def test_partitioned_op_equals_single_gpu(use_side):
-    """Shards of the sequence-partitioned op (NCCL all-gathers, chunked K/V kernel input, optional side
-    stream + own communicator for the large all-gather) are bit-equal to the single-GPU op: 100 views."""
+    """Shards of the sequence-partitioned op (chunked K/V kernel input; token-level exchange by an NCCL
+    all-gather, by one on a side stream with its own communicator, or by the copy engines over CUDA IPC)
+    are bit-equal to the single-GPU op: 100 views, run twice so that the second exchange reuses the buffers."""
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 8)
     if world < 2:
@@ -252,7 +258,7 @@ def test_partitioned_op_equals_single_gpu(use_side):
         world -= 1
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
-    port = 29500 + (os.getpid() % 500) + (1 if use_side else 0)
+    port = 29500 + (os.getpid() % 500) + ["nccl", "nccl-side", "peer"].index(use_side)
     procs = [ctx.Process(target=_partition_worker, args=(r, world, port, 100, use_side, result)) for r in range(world)]
     for pr in procs:
         pr.start()
