@@ -83,6 +83,18 @@ struct CmpParams {
   uint32_t* status;
 };
 
+// Index of the lowest set bit of a non-zero 16-bit mask, and the integer held exactly by a float in
+// [1, 2^16), both on the integer pipes: find-first-set, population count and float-to-int conversion
+// execute on the same 16-lane unit as the exponentials, which the softmax warps keep busy.
+__device__ __forceinline__ int lowbit16_alu(uint32_t m) {
+  const uint32_t b = m & (0u - m);
+  return ((b & 0xff00u) ? 8 : 0) + ((b & 0xf0f0u) ? 4 : 0) + ((b & 0xccccu) ? 2 : 0) + ((b & 0xaaaau) ? 1 : 0);
+}
+__device__ __forceinline__ uint32_t small_int_of_float(float f) {
+  const uint32_t b = __float_as_uint(f);
+  return ((b & 0x7fffffu) | 0x800000u) >> (150u - (b >> 23));
+}
+
 // Threshold for the float pre-filter `score > thr`: a score can only enter a full list if its key
 // is strictly greater than the key in slot topk-1 (an equal key loses to the older, smaller
 // column), so rows full of equal scores stop producing hits once their list is full.  The one
@@ -507,7 +519,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           left = false;
         }
         if (!__any_sync(0xffffffffu, left)) return;                // nothing left anywhere in the warp
-        uint32_t m = left ? __float2uint_rn(accf) : 0u;
+        uint32_t m = left ? small_int_of_float(accf) : 0u;
         if (m) {
           // this thread's own copy of the chunk, so that a hit can be fetched by its (dynamic) index
           uint4* s4 = reinterpret_cast<uint4*>(scratch);
@@ -516,7 +528,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         while (true) {
           while (m && cnt < kPend) {
-            const int e = __ffs(m) - 1;
+            const int e = lowbit16_alu(m);
             m &= m - 1;
             const float v = __uint_as_float(scratch[(((e >> 2) * 32 + lane) << 2) + (e & 3)]);
             my_pend[cnt * 32] = make_uint2(sortable_key(v), static_cast<uint32_t>(cbase + e));
