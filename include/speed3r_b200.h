@@ -211,6 +211,22 @@ int s3r_sel_attn_bwd(const void* q, const void* k, const void* v, const int32_t*
                      void* dq, void* dk, void* dv, int B, int H, int Tq, int Tk, int d, int block, int topk,
                      float scale, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Multi-GPU helper of the sequence-partitioned op (the reference is single-GPU: no counterpart).
+ * Copies `nseg` (<= 16) segments src[s] -> dst[s] of bytes[s] bytes (multiples of 16, 16-byte aligned)
+ * with one kernel of `ctas` CTAs.  The sources are meant to be PEER memory mapped into this process
+ * (CUDA IPC); they are only read, with plain loads.  A small `ctas` (16..32) keeps the copy on a few
+ * SMs so that it can run beside a kernel that fills all the others.
+ * ------------------------------------------------------------------------------------------ */
+int s3r_peer_pull(const void* const* src, void* const* dst, const int64_t* bytes, int nseg, int ctas, void* stream);
+
+/* CUDA IPC for those sources.  s3r_ipc_export: the 64-byte handle of the allocation that holds `ptr` and
+ * `ptr`'s offset in it (the owner keeps the buffer alive).  s3r_ipc_import: opens such a handle in another
+ * process of the same node WITH THE IMPORTER'S DEVICE CURRENT (lazy peer access), so that kernels of that
+ * device may dereference the returned address; the mapping lasts until the process exits. */
+int s3r_ipc_export(const void* ptr, void* handle64, int64_t* offset);
+int s3r_ipc_import(const void* handle64, int64_t offset, void** ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,9 +17,9 @@ The two attention callables are injected so that the host logic can be exercised
 
 The token-level exchange is the large one (2*T*H*d*2 bytes in total) and is only needed by the
 selection kernel, i.e. after the compression attention.  An NCCL all-gather moves it with CTAs that
-compete with the compression kernel for SMs; ``PeerGather`` moves it with the copy engines instead:
-every rank exposes its shard through CUDA IPC and pulls its peers' shards with plain device-to-device
-copies on side streams while the compression kernel owns every SM.
+compete with the compression kernel for SMs; ``PeerGather`` pulls it instead with a copy kernel of a
+few CTAs from buffers every rank exposes through CUDA IPC, launched just ahead of the compression
+kernel, which then has all the other SMs to itself from the start.
 """
 from __future__ import annotations
 
@@ -48,8 +48,11 @@ def all_gather_chunks(x: Tensor, group=None) -> Tensor:
     return out.view((world,) + tuple(x.shape))
 
 
+_IPC_BASE = {}      # (importing device, IPC handle) -> base address of the mapped allocation in this process
+
+
 class PeerGather:
-    """All-gather of equally shaped ``[B,H,n,d]`` shards by copy engines (one node, one process per GPU).
+    """All-gather of equally shaped ``[B,H,n,d]`` shards by peer loads (one node, one process per GPU).
 
     Every rank owns the result buffer ``out [G,B,H,n,d]`` (chunk g = rank g's shard, the layout the
     selection kernel reads in place) and has mapped its peers' result buffers through CUDA IPC; a rank
@@ -62,24 +65,44 @@ class PeerGather:
        ``out[rank]`` (a producer may instead write ``local()`` directly and call ``stage(None)``);
     2. some collective of the caller that every rank enters AFTER ``stage`` (here: the pooled all-gather)
        - once it has completed locally, every peer's shard is known to be written;
-    3. ``pull()`` - side streams wait for the current stream, then copy the peers' shards into ``out``
-       (device-to-device copies between GPUs: no SM is used);
+    3. ``pull()`` - a side stream waits for the current stream (or for a given event), then a copy kernel
+       of a few CTAs (``s3r_peer_pull``: plain loads from the peers, stores locally) fills ``out``;
     4. ``wait()`` - the current stream waits for the side streams; ``out`` is complete.
 
     Peers' memory is only ever the SOURCE of plain copies."""
 
-    def __init__(self, shape, dtype, device, group=None, n_streams: int = 4):
-        from torch.multiprocessing.reductions import reduce_tensor
+    def __init__(self, shape, dtype, device, group=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.shape = tuple(shape)
         self.out = torch.empty((self.world,) + self.shape, device=device, dtype=dtype)
         self._token = torch.zeros(1, device=device)
-        handles = [None] * self.world
-        dist.all_gather_object(handles, reduce_tensor(self.out), group=group)
-        self.peer_out = [self.out if g == self.rank else rebuild(*args) for g, (rebuild, args) in enumerate(handles)]
-        self.streams = [torch.cuda.Stream(device=device) for _ in range(max(1, min(n_streams, self.world - 1)))]
+        # Every rank exports its buffer (handle of the allocation + offset) and imports its peers' with its
+        # own device current: the addresses are then valid for kernels of THIS device.
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load()
+        with torch.cuda.device(device):
+            hbuf = C.create_string_buffer(64)
+            off = C.c_int64(0)
+            _lib.check(lib.s3r_ipc_export(self.out.data_ptr(), hbuf, C.byref(off)), "s3r_ipc_export")
+            mine = (hbuf.raw, int(off.value))
+            exported = [None] * self.world
+            dist.all_gather_object(exported, mine, group=group)
+            shard_bytes = self.out[0].numel() * self.out.element_size()
+            self.peer_ptr = []                       # device address of rank g's own shard inside rank g's buffer
+            for g, (handle, offset) in enumerate(exported):
+                if g == self.rank:
+                    self.peer_ptr.append(self.out[g].data_ptr())
+                    continue
+                key = (torch.device(device).index, handle)
+                if key not in _IPC_BASE:             # an allocation is opened once per process and device
+                    ptr = C.c_void_p(0)
+                    _lib.check(lib.s3r_ipc_import(handle, 0, C.byref(ptr)), "s3r_ipc_import")
+                    _IPC_BASE[key] = int(ptr.value)
+                self.peer_ptr.append(_IPC_BASE[key] + offset + g * shard_bytes)
+        self.streams = [torch.cuda.Stream(device=device, priority=-1)]
         self._done = [torch.cuda.Event() for _ in self.streams]
         dist.barrier(group=group)                    # every rank has mapped every buffer before first use
 
@@ -92,16 +115,30 @@ class PeerGather:
         if x is not None:
             self.out[self.rank].copy_(x)
 
-    def pull(self) -> Tensor:
+    def pull(self, after: Optional["torch.cuda.Event"] = None, ctas: int = 16) -> Tensor:
+        """Launch the copy kernel on the side stream; it starts once the current stream has reached this
+        point or, with ``after``, once that event has happened.  Call it BEFORE launching the kernel it is to
+        run beside: its few CTAs must be resident first."""
+        import ctypes as C
+        from . import _lib
         cur = torch.cuda.current_stream()
-        for st in self.streams:
+        st = self.streams[0]
+        if after is not None:
+            st.wait_event(after)
+        else:
             st.wait_stream(cur)
-        for i in range(1, self.world):                        # the ring after this rank: peers are hit evenly
+        n = self.world - 1
+        srcs = (C.c_void_p * n)()
+        dsts = (C.c_void_p * n)()
+        nbytes = (C.c_int64 * n)()
+        for i in range(1, self.world):                        # the ring after this rank
             g = (self.rank + i) % self.world
-            with torch.cuda.stream(self.streams[(i - 1) % len(self.streams)]):
-                self.out[g].copy_(self.peer_out[g][g], non_blocking=True)
-        for st, ev in zip(self.streams, self._done):
-            ev.record(st)
+            srcs[i - 1] = self.peer_ptr[g]
+            dsts[i - 1] = self.out[g].data_ptr()
+            nbytes[i - 1] = self.out[g].numel() * self.out.element_size()
+        with torch.cuda.device(self.out.device):
+            _lib.check(_lib.load().s3r_peer_pull(srcs, dsts, nbytes, n, ctas, st.cuda_stream), "s3r_peer_pull")
+        self._done[0].record(st)
         return self.out
 
     def wait(self) -> Tensor:
@@ -149,7 +186,7 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
         q_c, k_c, v_c = pooled_local()
         kc_all = chunks_to_dense(all_gather_chunks(k_c, group))
         vc_all = chunks_to_dense(all_gather_chunks(v_c, group))
-        pk.pull()
+        pk.pull()                                              # few CTAs, resident before the attention kernel
         pv.pull()
         o_c, idx = cmp_attn_topk(q_c, kc_all, vc_all, topk)
         k_all, v_all = pk.wait(), pv.wait()
