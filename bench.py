@@ -174,7 +174,7 @@ def workload_config(args):
     return {"workload": f"sparse global-attention op, {args.mode}, {args.views} views x {TOK_PER_VIEW} tokens "
                         f"(T={T}), H={H}, d={D}, pool {BS}/{BS}, select block {BS}, top-{TOPK}, {getattr(args, 'inputs', 'iid')} inputs",
             "tokens": T, "views": args.views, "mode": args.mode,
-            "parallelism": (f"sp{args.gpus}, token K/V exchange: " + ("copy engines over CUDA IPC" if getattr(args, "gather", "peer") == "peer"
+            "parallelism": (f"sp{args.gpus}, token K/V exchange: " + ("peer pull kernel over CUDA IPC" if getattr(args, "gather", "nccl") == "peer"
                                                                        else "NCCL all-gather on a side stream")) if args.gpus > 1 else "single",
             "l2": "inputs (q,k,v: 3 x %.1f GB) larger than the 126 MB L2" % (T * H * D * 2 / 1e9)}
 
@@ -409,8 +409,9 @@ def main():
                          "attention class swapped in; prints a line of its own (metric pi3_sparse_forward_views_per_s)")
     ap.add_argument("--model-attn", default="ours", choices=["ours", "reference"],
                     help="--model: which attention class the global blocks use (reference = its Triton module, 1 GPU only)")
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: token-level K/V exchange by copy engines over CUDA IPC (peer) or an NCCL all-gather")
+    ap.add_argument("--gather", default="nccl", choices=["peer", "nccl"],
+                    help="N > 1: token-level K/V exchange by an NCCL all-gather on a side stream (default, measured "
+                         "fastest) or by this library's peer pull kernel over CUDA IPC")
     ap.add_argument("--no-triton-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()

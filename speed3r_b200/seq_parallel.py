@@ -224,7 +224,7 @@ class SequenceParallel:
     prologue (split, LayerNorm, rotary embedding, pooling) stays local; this object does the exchange.
     Forward only (inference)."""
 
-    def __init__(self, group=None, gather: str = "peer"):
+    def __init__(self, group=None, gather: str = "nccl"):
         self.group = group
         self.gather = gather
         self._peer = {}
