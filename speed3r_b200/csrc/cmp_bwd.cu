@@ -1,145 +1,319 @@
-// Compression branch, backward: dense flash-attention backward over the pooled tensors.
-//   delta = sum_d o*do ; dQ kernel: CTA = 128 query rows x all key tiles of 64 ;
-//   dK/dV kernel: CTA = 128 key rows x all query tiles of 64.
-// Tiles are shared by the CTA's 8 warps through a two-stage cp.async ring; the arithmetic is the
-// mma.sync building blocks of bwd_common.cuh (P and dS are rounded to bf16 before the second
-// products, like the reference kernels).
-#include "bwd_common.cuh"
+// Compression branch, backward: dense flash-attention backward over the pooled tensors on the
+// tensor-memory MMA (tcgen05), operands staged by TMA.
+//
+//   delta = sum_d o*do                                  (s3r_delta)
+//   dK/dV kernel: a CTA owns 128 key rows and streams all query tiles of 64 rows
+//        S^T = K Q^T, dP^T = V dO^T                     (M=128 keys, N=64 queries, K=64)
+//        P^T = exp2(S^T*c - lse[q]),  dS^T = P^T * (dP^T - delta[q])        thread = key row
+//        dV += P^T dO,  dK += dS^T Q                    (M=128, N=64, K=64 queries; A from tensor memory)
+//   dQ kernel: a CTA owns 128 query rows and streams all key tiles of 64 rows
+//        S = Q K^T, dP = dO V^T;  dS = exp2(S*c - lse[row]) * (dP - delta[row]);  dQ += dS K
+// P and dS are rounded to bf16 before the second products, like the reference kernels
+// (flash_attention_topk.py:246-512); the softmax scale of dS is applied once, to the dK / dQ accumulators.
+//
+// One template covers both: the CTA's own tiles X0, X1 (128 rows; K,V or Q,dO) are the A operands of the
+// first products, the streamed tiles Y0, Y1 (64 rows; Q,dO or K,V) their B operands (K-major) and, read
+// with the other descriptor, the B operands of the second products (N contiguous).
+// Roles: warp 0 TMA producer, warp 1 tcgen05.mma issuer, warp 2 tensor-memory allocator, warp 3 loads the
+// streamed rows' lse/delta (dK/dV kernel), warps 4-7 and 8-11 two compute warpgroups working on alternate
+// streamed tiles, each with its own S/dP/P/dS buffers in tensor memory - so the MMAs of tile i+1 run under
+// the exponentials of tile i.  Bound: the exponentials (64 per thread and tile, 16 per clock and SM), as in
+// the forward kernel; P is recomputed in both kernels.
+#include "common.cuh"
 
 namespace s3r {
 
-constexpr int kCbWarps = 8;
-constexpr int kCbRows = kCbWarps * 16;        // rows owned by a CTA
-constexpr int kCbTile = 64;                   // rows per streamed tile
-constexpr int kCbTileBytes = kCbTile * kPitch;
-constexpr int kCbStageBytes = 2 * kCbTileBytes;
+constexpr int kCbThreads = 384;
+constexpr int kCbStages = 4;
+constexpr int kCbOwnBytes = 128 * 128;        // 128 rows x 64 bf16
+constexpr int kCbStrBytes = 64 * 128;         // 64 rows x 64 bf16
+constexpr int kCbOffX = 0;                                    // X0, X1
+constexpr int kCbOffY = 2 * kCbOwnBytes;                      // ring of (Y0, Y1)
+constexpr int kCbOffStat = kCbOffY + kCbStages * 2 * kCbStrBytes;   // ring of 64 x (lse2, delta)
+constexpr int kCbSmemBytes = kCbOffStat + kCbStages * 128 * 4 + 1024;
+// tensor-memory columns (per compute warpgroup w = 0, 1)
+constexpr uint32_t kCbColS = 0, kCbColDP = 128, kCbColP = 256, kCbColDS = 320, kCbColAcc0 = 384, kCbColAcc1 = 448;
 
-struct CmpBwdParams {
-  const __nv_bfloat16 *q, *k, *v, *d_o;
-  const float *lse, *delta;
-  __nv_bfloat16 *dq, *dk, *dv;
-  int Nq, Nc;
-  float cs, scale;
+struct CbCtl {
+  uint64_t x_full, o_full;
+  uint64_t y_full[kCbStages], y_empty[kCbStages], st_full[kCbStages];
+  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
 };
 
-// `rows` rows x 128 B -> padded tile, all 256 threads; rows >= nrows zero-filled
-__device__ __forceinline__ void cta_load_tile(uint32_t dst, const __nv_bfloat16* src, int rows, int nrows, int tid) {
-  for (int ch = tid; ch < rows * 8; ch += kCbWarps * 32) {
-    const int r = ch >> 3, c16 = ch & 7;
-    cp_async16(dst + r * kPitch + c16 * 16, src + static_cast<int64_t>(r) * 64 + c16 * 8, r < nrows);
-  }
-}
+struct CbParams {
+  const float *lse, *delta;      // [BH, Nq]
+  __nv_bfloat16 *out0, *out1;    // dK/dV kernel: dV, dK [BH, Nc, 64];  dQ kernel: dQ [BH, Nq, 64], unused
+  int n_own, n_str;              // rows of the owned and of the streamed tensors (Nc, Nq | Nq, Nc)
+  int Nq;
+  float cs, scale;               // softmax scale * log2(e), softmax scale
+  uint32_t* status;
+};
 
-__global__ void __launch_bounds__(kCbWarps * 32) cmp_bwd_dq_kernel(const CmpBwdParams p) {
-  __shared__ __align__(16) uint8_t smem[2][kCbStageBytes];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
-  const int ctas = (p.Nq + kCbRows - 1) / kCbRows;
-  const int bh = blockIdx.x / ctas;
-  const int row0 = (blockIdx.x % ctas) * kCbRows;
-  const uint32_t sm[2] = {smem_u32(&smem[0][0]), smem_u32(&smem[1][0])};
-
-  // Q (stage 0) and dO (stage 1): 128 rows each
-  cta_load_tile(sm[0], p.q + (static_cast<int64_t>(bh) * p.Nq + row0) * 64, kCbRows, p.Nq - row0, threadIdx.x);
-  cta_load_tile(sm[1], p.d_o + (static_cast<int64_t>(bh) * p.Nq + row0) * 64, kCbRows, p.Nq - row0, threadIdx.x);
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
-  uint32_t qf[4][4], dof[4][4];
-  load_a_frags(qf, sm[0] + warp * 16 * kPitch, lane);
-  load_a_frags(dof, sm[1] + warp * 16 * kPitch, lane);
-  __syncthreads();
-  float lse2[2], delta[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int t = row0 + warp * 16 + g + 8 * r;
-    lse2[r] = (t < p.Nq) ? p.lse[static_cast<int64_t>(bh) * p.Nq + t] * 1.4426950408889634f : INFINITY;
-    delta[r] = (t < p.Nq) ? p.delta[static_cast<int64_t>(bh) * p.Nq + t] : 0.f;
-  }
-  float dq[8][4] = {};
-  const __nv_bfloat16* Kb = p.k + static_cast<int64_t>(bh) * p.Nc * 64;
-  const __nv_bfloat16* Vb = p.v + static_cast<int64_t>(bh) * p.Nc * 64;
-  const int ntiles = (p.Nc + kCbTile - 1) / kCbTile;
-  auto prefetch = [&](int it) {
-    const int k0 = it * kCbTile;
-    cta_load_tile(sm[it & 1], Kb + static_cast<int64_t>(k0) * 64, kCbTile, p.Nc - k0, threadIdx.x);
-    cta_load_tile(sm[it & 1] + kCbTileBytes, Vb + static_cast<int64_t>(k0) * 64, kCbTile, p.Nc - k0, threadIdx.x);
-    cp_async_commit();
-  };
-  prefetch(0);
-  for (int it = 0; it < ntiles; ++it) {
-    if (it + 1 < ntiles) { prefetch(it + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-    __syncthreads();
-    const uint32_t cur = sm[it & 1];
-#pragma unroll
-    for (int sb = 0; sb < kCbTile / 16; ++sb) {
-      const int kv = p.Nc - (it * kCbTile + sb * 16);
-      if (kv > 0)
-        pair_dq(qf, dof, lse2, delta, cur + sb * 16 * kPitch, cur + kCbTileBytes + sb * 16 * kPitch, min(16, kv), p.cs,
-                p.scale, dq, lane);
-    }
-    __syncthreads();
-  }
-  const int wrow0 = row0 + warp * 16;
-  __nv_bfloat16* out = p.dq + (static_cast<int64_t>(bh) * p.Nq + wrow0) * 64;
-  store_acc_bf16(dq, [&](int r) { return (wrow0 + r < p.Nq) ? out + r * 64 : nullptr; }, lane);
-}
-
-__global__ void __launch_bounds__(kCbWarps * 32, 2) cmp_bwd_dkdv_kernel(const CmpBwdParams p) {
-  __shared__ __align__(16) uint8_t smem[2][kCbStageBytes];
-  __shared__ float stats[2][2 * kCbTile];      // [stage][lse2 x64 | delta x64]
+// MODE 0: dK/dV (own = K, V; streamed = Q, dO).  MODE 1: dQ (own = Q, dO; streamed = K, V).
+template <int MODE>
+__global__ void __launch_bounds__(kCbThreads, 1)
+cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant__ CUtensorMap map_x1,
+               const __grid_constant__ CUtensorMap map_y0, const __grid_constant__ CUtensorMap map_y1, const CbParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ CbCtl ctl;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ctas = (p.Nc + kCbRows - 1) / kCbRows;
-  const int bh = blockIdx.x / ctas;
-  const int row0 = (blockIdx.x % ctas) * kCbRows;
-  const uint32_t sm[2] = {smem_u32(&smem[0][0]), smem_u32(&smem[1][0])};
+  const int own_tiles = (p.n_own + 127) / 128;
+  const int bh = blockIdx.x / own_tiles;
+  const int r0 = (blockIdx.x % own_tiles) * 128;
+  const int ntiles = (p.n_str + 63) / 64;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
+  float* stats = reinterpret_cast<float*>(sptr + kCbOffStat);        // [stage][lse2 x64 | delta x64]
 
-  cta_load_tile(sm[0], p.k + (static_cast<int64_t>(bh) * p.Nc + row0) * 64, kCbRows, p.Nc - row0, threadIdx.x);
-  cta_load_tile(sm[1], p.v + (static_cast<int64_t>(bh) * p.Nc + row0) * 64, kCbRows, p.Nc - row0, threadIdx.x);
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
-  uint32_t kf[4][4], vf[4][4];
-  load_a_frags(kf, sm[0] + warp * 16 * kPitch, lane);
-  load_a_frags(vf, sm[1] + warp * 16 * kPitch, lane);
-  __syncthreads();
-
-  float dk[8][4] = {}, dv[8][4] = {};
-  const __nv_bfloat16* Qb = p.q + static_cast<int64_t>(bh) * p.Nq * 64;
-  const __nv_bfloat16* Db = p.d_o + static_cast<int64_t>(bh) * p.Nq * 64;
-  const float* Lb = p.lse + static_cast<int64_t>(bh) * p.Nq;
-  const float* Eb = p.delta + static_cast<int64_t>(bh) * p.Nq;
-  const int ntiles = (p.Nq + kCbTile - 1) / kCbTile;
-  auto prefetch = [&](int it) {
-    const int q0 = it * kCbTile;
-    cta_load_tile(sm[it & 1], Qb + static_cast<int64_t>(q0) * 64, kCbTile, p.Nq - q0, threadIdx.x);
-    cta_load_tile(sm[it & 1] + kCbTileBytes, Db + static_cast<int64_t>(q0) * 64, kCbTile, p.Nq - q0, threadIdx.x);
-    cp_async_commit();
-    if (threadIdx.x < 2 * kCbTile) {
-      const int t = q0 + (threadIdx.x & (kCbTile - 1));
-      float val;
-      if (threadIdx.x < kCbTile) val = (t < p.Nq) ? Lb[t] * 1.4426950408889634f : INFINITY;
-      else val = (t < p.Nq) ? Eb[t] : 0.f;
-      stats[it & 1][threadIdx.x] = val;
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    mbar_init(&ctl.x_full, 1);
+    mbar_init(&ctl.o_full, 1);
+    for (int s = 0; s < kCbStages; ++s) {
+      mbar_init(&ctl.y_full[s], 1);
+      mbar_init(&ctl.y_empty[s], 1);
+      mbar_init(&ctl.st_full[s], 1);
     }
-  };
-  prefetch(0);
-  for (int it = 0; it < ntiles; ++it) {
-    if (it + 1 < ntiles) { prefetch(it + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-    __syncthreads();
-    const uint32_t cur = sm[it & 1];
-#pragma unroll
-    for (int sb = 0; sb < kCbTile / 16; ++sb) {
-      if (it * kCbTile + sb * 16 < p.Nq)
-        pair_dkdv(kf, vf, cur + sb * 16 * kPitch, cur + kCbTileBytes + sb * 16 * kPitch, &stats[it & 1][sb * 16],
-                  &stats[it & 1][kCbTile + sb * 16], p.cs, p.scale, dk, dv, lane);
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(&ctl.s_full[w], 1);
+      mbar_init(&ctl.p_full[w], 128);
+      mbar_init(&ctl.pv_done[w], 1);
     }
-    __syncthreads();
+    mbar_fence_init();
   }
-  const int wrow0 = row0 + warp * 16;
-  __nv_bfloat16* okp = p.dk + (static_cast<int64_t>(bh) * p.Nc + wrow0) * 64;
-  __nv_bfloat16* ovp = p.dv + (static_cast<int64_t>(bh) * p.Nc + wrow0) * 64;
-  store_acc_bf16(dk, [&](int r) { return (wrow0 + r < p.Nc) ? okp + r * 64 : nullptr; }, lane);
-  store_acc_bf16(dv, [&](int r) { return (wrow0 + r < p.Nc) ? ovp + r * 64 : nullptr; }, lane);
+  if (warp == 2) {
+    tmem_alloc(&ctl.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl.tmem_base;
+  volatile uint32_t* abort_flag = &ctl.abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&ctl.x_full, 2 * kCbOwnBytes);
+      tma_load_3d(sbase + kCbOffX, &map_x0, &ctl.x_full, 0, r0, bh);
+      tma_load_3d(sbase + kCbOffX + kCbOwnBytes, &map_x1, &ctl.x_full, 0, r0, bh);
+      int issued = 0;
+      for (int i = 0; i < ntiles; ++i) {
+        const int s = i % kCbStages;
+        if (!mbar_wait(&ctl.y_empty[s], ((i / kCbStages) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&ctl.y_full[s], 2 * kCbStrBytes);
+        tma_load_3d(sbase + kCbOffY + s * 2 * kCbStrBytes, &map_y0, &ctl.y_full[s], 0, i * 64, bh);
+        tma_load_3d(sbase + kCbOffY + s * 2 * kCbStrBytes + kCbStrBytes, &map_y1, &ctl.y_full[s], 0, i * 64, bh);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // give copies already in flight a bounded chance to land before the CTA's memory is released
+        for (int i = max(0, issued - kCbStages); i < issued; ++i) {
+          volatile uint32_t dummy = 0;
+          mbar_wait(&ctl.y_full[i % kCbStages], (i / kCbStages) & 1, &dummy);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_1 = umma_idesc_bf16(128, 64, 0, 0);    // both operands K-major
+      constexpr uint32_t idesc_2 = umma_idesc_bf16(128, 64, 0, 1);    // B = streamed tile read as [rows][64]: N contiguous
+      auto first = [&](int w, int s) {            // S[w] = X0 Y0^T, dP[w] = X1 Y1^T
+        const uint32_t y = sbase + kCbOffY + s * 2 * kCbStrBytes;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + kCbColS + w * 64, umma_desc_sw128(sbase + kCbOffX + ks * 32), umma_desc_sw128(y + ks * 32), idesc_1, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + kCbColDP + w * 64, umma_desc_sw128(sbase + kCbOffX + kCbOwnBytes + ks * 32),
+                  umma_desc_sw128(y + kCbStrBytes + ks * 32), idesc_1, ks > 0);
+      };
+      auto second = [&](int w, int s, bool acc) {
+        const uint32_t y = sbase + kCbOffY + s * 2 * kCbStrBytes;
+        if (MODE == 0) {                          // dV += P^T dO (Y1),  dK += dS^T Q (Y0)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ts(tmem + kCbColAcc0, tmem + kCbColP + w * 32 + ks * 8, umma_desc_sw128(y + kCbStrBytes + ks * 2048), idesc_2,
+                    (acc || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)            // dK += dS^T Q   |   dQ += dS K      (Y0)
+          umma_ts(tmem + kCbColAcc1, tmem + kCbColDS + w * 32 + ks * 8, umma_desc_sw128(y + ks * 2048), idesc_2,
+                  (acc || ks > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(&ctl.x_full, 0, abort_flag);
+      for (int i = 0; i <= ntiles && ok; ++i) {
+        if (i < ntiles) {
+          // S and dP of this warpgroup were last read for tile i-2, whose p_full this thread has waited for
+          const int s = i % kCbStages;
+          ok = mbar_wait(&ctl.y_full[s], (i / kCbStages) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          first(i & 1, s);
+          umma_commit(&ctl.s_full[i & 1]);
+        }
+        if (i >= 1) {
+          const int k = i - 1, w = k & 1, s = k % kCbStages;
+          ok = mbar_wait(&ctl.p_full[w], (k >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          second(w, s, k > 0);
+          umma_commit(&ctl.pv_done[w]);           // P and dS of this warpgroup may be overwritten
+          umma_commit(&ctl.y_empty[s]);
+        }
+      }
+      umma_commit(&ctl.o_full);
+      if (!ok) {
+        volatile uint32_t dummy = 0;
+        mbar_wait(&ctl.o_full, 0, &dummy);        // let issued MMAs drain before tensor memory is freed
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ lse / delta of the streamed rows (dK/dV kernel)
+    if (MODE == 0) {
+      for (int i = 0; i < ntiles; ++i) {
+        const int s = i % kCbStages;
+        if (!mbar_wait_warp(&ctl.y_empty[s], ((i / kCbStages) & 1) ^ 1, abort_flag)) break;
+        float* dst = stats + s * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int q = i * 64 + h * 32 + lane;
+          const bool in = q < p.n_str;
+          // rows past the end: lse = +inf makes P exactly 0
+          dst[h * 32 + lane] = in ? p.lse[static_cast<int64_t>(bh) * p.Nq + q] * 1.4426950408889634f : INFINITY;
+          dst[64 + h * 32 + lane] = in ? p.delta[static_cast<int64_t>(bh) * p.Nq + q] : 0.f;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.st_full[s]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ compute, thread = owned row
+    const int w = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int row = r0 + quarter * 32 + lane;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t t_s = lane_base + kCbColS + w * 64, t_dp = lane_base + kCbColDP + w * 64;
+    const uint32_t t_p = lane_base + kCbColP + w * 32, t_ds = lane_base + kCbColDS + w * 32;
+    const float cs = p.cs;
+    float my_lse2 = INFINITY, my_delta = 0.f;       // dQ kernel: this row's statistics
+    if (MODE == 1 && row < p.n_own) {
+      my_lse2 = p.lse[static_cast<int64_t>(bh) * p.Nq + row] * 1.4426950408889634f;
+      my_delta = p.delta[static_cast<int64_t>(bh) * p.Nq + row];
+    }
+    bool ok = true;
+    for (int i = w; i < ntiles; i += 2) {
+      const int s = i % kCbStages;
+      const uint32_t ph = (i >> 1) & 1;
+      if (!mbar_wait_warp(&ctl.s_full[w], ph, abort_flag)) { ok = false; break; }
+      if (MODE == 0 && !mbar_wait_warp(&ctl.st_full[s], (i / kCbStages) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      // P and dS of tile i-2 must have been consumed by their MMAs before they are overwritten
+      if (i >= 2) {
+        if (!mbar_wait_warp(&ctl.pv_done[w], ph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+      }
+      const float4* st4 = reinterpret_cast<const float4*>(stats + s * 128);
+      auto process = [&](uint32_t (&xs)[16], uint32_t (&xd)[16], int c) {
+        uint32_t pk[8], dk[8];
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+          float l4[4], d4[4];
+          if (MODE == 0) {
+            const float4 a = st4[c * 4 + g4], b = st4[16 + c * 4 + g4];     // same address in every lane: broadcast
+            l4[0] = a.x; l4[1] = a.y; l4[2] = a.z; l4[3] = a.w;
+            d4[0] = b.x; d4[1] = b.y; d4[2] = b.z; d4[3] = b.w;
+          } else {
+            l4[0] = l4[1] = l4[2] = l4[3] = my_lse2;
+            d4[0] = d4[1] = d4[2] = d4[3] = my_delta;
+          }
+          float pv[4], dv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            pv[e] = fast_exp2(fmaf(__uint_as_float(xs[4 * g4 + e]), cs, -l4[e]));
+            dv[e] = pv[e] * (__uint_as_float(xd[4 * g4 + e]) - d4[e]);
+          }
+          pk[2 * g4] = pack_bf16(pv[0], pv[1]);
+          pk[2 * g4 + 1] = pack_bf16(pv[2], pv[3]);
+          dk[2 * g4] = pack_bf16(dv[0], dv[1]);
+          dk[2 * g4 + 1] = pack_bf16(dv[2], dv[3]);
+        }
+        if (MODE == 0) tmem_st8(t_p + c * 8, pk);
+        tmem_st8(t_ds + c * 8, dk);
+      };
+      // tensor-memory loads run one chunk ahead of the arithmetic
+      uint32_t sa[16], da[16], sb[16], db[16];
+      tmem_ld16(t_s, sa);
+      tmem_ld16(t_dp, da);
+#pragma unroll 1
+      for (int c = 0; c < 4; c += 2) {
+        tmem_ld_wait();
+        tmem_ld16(t_s + (c + 1) * 16, sb);
+        tmem_ld16(t_dp + (c + 1) * 16, db);
+        process(sa, da, c);
+        tmem_ld_wait();
+        if (c + 2 < 4) {
+          tmem_ld16(t_s + (c + 2) * 16, sa);
+          tmem_ld16(t_dp + (c + 2) * 16, da);
+        }
+        process(sb, db, c + 1);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&ctl.p_full[w]);
+    }
+    // epilogue: the accumulators -> bf16.  dK/dV kernel: warpgroup 0 stores dV, warpgroup 1 dK (scaled);
+    // dQ kernel: each warpgroup stores one half of dQ's channels (scaled).
+    if (ok) ok = mbar_wait_warp(&ctl.o_full, 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      if (MODE == 0) {
+        const uint32_t t_acc = lane_base + (w == 0 ? kCbColAcc0 : kCbColAcc1);
+        const float f = (w == 0) ? 1.f : p.scale;
+        __nv_bfloat16* out = (w == 0 ? p.out0 : p.out1) + (static_cast<int64_t>(bh) * p.n_own + row) * 64;
+#pragma unroll 1
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t o[32];
+          tmem_ld32(t_acc + hf * 32, o);
+          tmem_ld_wait();
+          if (row < p.n_own) {
+            uint4* dst = reinterpret_cast<uint4*>(out + hf * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              dst[v] = make_uint4(pack_bf16(__uint_as_float(o[8 * v]) * f, __uint_as_float(o[8 * v + 1]) * f),
+                                  pack_bf16(__uint_as_float(o[8 * v + 2]) * f, __uint_as_float(o[8 * v + 3]) * f),
+                                  pack_bf16(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f),
+                                  pack_bf16(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f));
+          }
+        }
+      } else {
+        uint32_t o[32];
+        tmem_ld32(lane_base + kCbColAcc1 + w * 32, o);
+        tmem_ld_wait();
+        if (row < p.n_own) {
+          const float f = p.scale;
+          uint4* dst = reinterpret_cast<uint4*>(p.out0 + (static_cast<int64_t>(bh) * p.n_own + row) * 64 + w * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            dst[v] = make_uint4(pack_bf16(__uint_as_float(o[8 * v]) * f, __uint_as_float(o[8 * v + 1]) * f),
+                                pack_bf16(__uint_as_float(o[8 * v + 2]) * f, __uint_as_float(o[8 * v + 3]) * f),
+                                pack_bf16(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f),
+                                pack_bf16(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f));
+        }
+      }
+    }
+    if (!ok) {
+      *abort_flag = 1u;
+      if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace s3r
@@ -153,24 +327,51 @@ extern "C" int s3r_cmp_attn_bwd(const void* q_c, const void* k_c, const void* v_
               "s3r_cmp_attn_bwd: NULL pointer");
   S3R_REQUIRE(B > 0 && H > 0 && Nq > 0 && Nc > 0, S3R_ERR_SHAPE, "s3r_cmp_attn_bwd: bad sizes");
   S3R_REQUIRE(d == 64, S3R_ERR_UNSUPPORTED, "s3r_cmp_attn_bwd: head_dim %d not supported (64 only)", d);
+  const uintptr_t al = reinterpret_cast<uintptr_t>(q_c) | reinterpret_cast<uintptr_t>(k_c) | reinterpret_cast<uintptr_t>(v_c) |
+                       reinterpret_cast<uintptr_t>(do_c) | reinterpret_cast<uintptr_t>(dq_c) |
+                       reinterpret_cast<uintptr_t>(dk_c) | reinterpret_cast<uintptr_t>(dv_c);
+  S3R_REQUIRE((al & 15) == 0, S3R_ERR_ALIGNMENT, "s3r_cmp_attn_bwd: tensors must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = s3r_delta(o_c, do_c, delta, static_cast<int64_t>(B) * H * Nq, d, stream);
   if (rc) return rc;
-  CmpBwdParams p;
-  p.q = static_cast<const __nv_bfloat16*>(q_c);
-  p.k = static_cast<const __nv_bfloat16*>(k_c);
-  p.v = static_cast<const __nv_bfloat16*>(v_c);
-  p.d_o = static_cast<const __nv_bfloat16*>(do_c);
+  const int BH = B * H;
+  CUtensorMap mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64;
+  {
+    uint32_t box128[3] = {64, 128, 1}, box64[3] = {64, 64, 1};
+    uint64_t dq_[3] = {64, static_cast<uint64_t>(Nq), static_cast<uint64_t>(BH)};
+    uint64_t sq_[2] = {128, static_cast<uint64_t>(Nq) * 128};
+    uint64_t dk_[3] = {64, static_cast<uint64_t>(Nc), static_cast<uint64_t>(BH)};
+    uint64_t sk_[2] = {128, static_cast<uint64_t>(Nc) * 128};
+    struct { CUtensorMap* m; const void* ptr; uint64_t* dims; uint64_t* strides; uint32_t* box; } maps[8] = {
+        {&mq128, q_c, dq_, sq_, box128}, {&mdo128, do_c, dq_, sq_, box128}, {&mk128, k_c, dk_, sk_, box128},
+        {&mv128, v_c, dk_, sk_, box128}, {&mq64, q_c, dq_, sq_, box64},     {&mdo64, do_c, dq_, sq_, box64},
+        {&mk64, k_c, dk_, sk_, box64},   {&mv64, v_c, dk_, sk_, box64}};
+    for (auto& e : maps) {
+      rc = make_tensor_map(e.m, e.ptr, 3, e.dims, e.strides, e.box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+    }
+  }
+  CbParams p;
   p.lse = lse; p.delta = delta;
-  p.dq = static_cast<__nv_bfloat16*>(dq_c);
-  p.dk = static_cast<__nv_bfloat16*>(dk_c);
-  p.dv = static_cast<__nv_bfloat16*>(dv_c);
-  p.Nq = Nq; p.Nc = Nc;
+  p.Nq = Nq;
   p.cs = scale * 1.4426950408889634f;
   p.scale = scale;
-  const int BH = B * H;
-  cmp_bwd_dkdv_kernel<<<BH * ((Nc + kCbRows - 1) / kCbRows), kCbWarps * 32, 0, st>>>(p);
-  cmp_bwd_dq_kernel<<<BH * ((Nq + kCbRows - 1) / kCbRows), kCbWarps * 32, 0, st>>>(p);
+  p.status = device_status_ptr();
+  S3R_REQUIRE(p.status != nullptr, S3R_ERR_DRIVER, "s3r_cmp_attn_bwd: could not resolve the device status word");
+  S3R_CUDA(cudaFuncSetAttribute(cmp_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCbSmemBytes));
+  S3R_CUDA(cudaFuncSetAttribute(cmp_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCbSmemBytes));
+  // dK, dV: own = K, V (Nc rows), streamed = Q, dO (Nq rows)
+  p.out0 = static_cast<__nv_bfloat16*>(dv_c);
+  p.out1 = static_cast<__nv_bfloat16*>(dk_c);
+  p.n_own = Nc; p.n_str = Nq;
+  const int64_t g0 = static_cast<int64_t>(BH) * ((Nc + 127) / 128), g1 = static_cast<int64_t>(BH) * ((Nq + 127) / 128);
+  S3R_REQUIRE(g0 < (1ll << 31) && g1 < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_cmp_attn_bwd: grid too large");
+  cmp_bwd_kernel<0><<<static_cast<unsigned>(g0), kCbThreads, kCbSmemBytes, st>>>(mk128, mv128, mq64, mdo64, p);
+  // dQ: own = Q, dO (Nq rows), streamed = K, V (Nc rows)
+  p.out0 = static_cast<__nv_bfloat16*>(dq_c);
+  p.out1 = nullptr;
+  p.n_own = Nq; p.n_str = Nc;
+  cmp_bwd_kernel<1><<<static_cast<unsigned>(g1), kCbThreads, kCbSmemBytes, st>>>(mq128, mdo128, mk64, mv64, p);
   S3R_CUDA(cudaGetLastError());
   return 0;
 }

@@ -315,9 +315,9 @@ def test_cmp_attn_backward_golden(name):
     assert_bf16_close(vg.grad, vr.grad, "dv_c")
 
 
-def test_cmp_attn_backward_seeded_rect():
+@pytest.mark.parametrize("B,H,Nq,Nc", [(2, 2, 203, 391), (1, 2, 1100, 777), (1, 1, 40, 50), (1, 1, 64, 17)])
+def test_cmp_attn_backward_seeded_rect(B, H, Nq, Nc):
     from speed3r_b200 import ops
-    B, H, Nq, Nc = 2, 2, 203, 391
     q, k, v, do = bf16_round(randn(71, B, H, Nq, 64), randn(72, B, H, Nc, 64), randn(73, B, H, Nc, 64),
                              randn(74, B, H, Nq, 64))
     qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
