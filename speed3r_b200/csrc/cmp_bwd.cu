@@ -2,49 +2,54 @@
 // tensor-memory MMA (tcgen05), operands staged by TMA.
 //
 //   delta = sum_d o*do                                  (s3r_delta)
-//   dK/dV kernel: a CTA owns 128 key rows and streams all query tiles of 64 rows
+//   dK/dV kernel: a CTA owns 256 key rows (two M=128 row tiles) and streams all query tiles of 64 rows
 //        S^T = K Q^T, dP^T = V dO^T                     (M=128 keys, N=64 queries, K=64)
 //        P^T = exp2(S^T*c - lse[q]),  dS^T = P^T * (dP^T - delta[q])        thread = key row
 //        dV += P^T dO,  dK += dS^T Q                    (M=128, N=64, K=64 queries; A from tensor memory)
-//   dQ kernel: a CTA owns 128 query rows and streams all key tiles of 64 rows
+//   dQ kernel: a CTA owns 256 query rows and streams all key tiles of 64 rows
 //        S = Q K^T, dP = dO V^T;  dS = exp2(S*c - lse[row]) * (dP - delta[row]);  dQ += dS K
 // P and dS are rounded to bf16 before the second products, like the reference kernels
 // (flash_attention_topk.py:246-512); the softmax scale of dS is applied once, to the dK / dQ accumulators.
 //
-// One template covers both: the CTA's own tiles X0, X1 (128 rows; K,V or Q,dO) are the A operands of the
-// first products, the streamed tiles Y0, Y1 (64 rows; Q,dO or K,V) their B operands (K-major) and, read
-// with the other descriptor, the B operands of the second products (N contiguous).
+// One template covers both: the CTA's own tiles X0, X1 (K,V or Q,dO) are the A operands of the first
+// products, the streamed tiles Y0, Y1 (64 rows; Q,dO or K,V) their B operands (K-major) and, read with
+// the other descriptor, the B operands of the second products (N contiguous).
+// What bounds the kernels is the streamed operand traffic from L2 (every CTA reads the whole streamed
+// tensors): bytes per score = 256 / owned rows, so a CTA owns 256 rows - as many as tensor memory holds
+// accumulators for (2 row tiles x (dK, dV) x 64 columns = 256 columns; the other 256 hold S and dP).
 // Roles: warp 0 TMA producer, warp 1 tcgen05.mma issuer, warp 2 tensor-memory allocator, warp 3 loads the
-// streamed rows' lse/delta (dK/dV kernel), warps 4-7 and 8-11 two compute warpgroups working on alternate
-// streamed tiles, each with its own S/dP/P/dS buffers in tensor memory - so the MMAs of tile i+1 run under
-// the exponentials of tile i.  Bound: the exponentials (64 per thread and tile, 16 per clock and SM), as in
-// the forward kernel; P is recomputed in both kernels.
+// streamed rows' lse/delta (dK/dV kernel), warps 4-7 and 8-11 one compute warpgroup per row tile.  P and dS
+// are written in place, over the low columns of S and dP (a thread's bf16 chunk c covers columns
+// 8c..8c+7, all of which it has already read as part of fp32 chunk c/2).  The two row tiles run in
+// antiphase: the MMAs of one are issued while the other is in its exponentials.
 #include "common.cuh"
 
 namespace s3r {
 
 constexpr int kCbThreads = 384;
-constexpr int kCbStages = 4;
+constexpr int kCbStages = 6;
+constexpr int kCbOwnRows = 256;
 constexpr int kCbOwnBytes = 128 * 128;        // 128 rows x 64 bf16
 constexpr int kCbStrBytes = 64 * 128;         // 64 rows x 64 bf16
-constexpr int kCbOffX = 0;                                    // X0, X1
-constexpr int kCbOffY = 2 * kCbOwnBytes;                      // ring of (Y0, Y1)
+constexpr int kCbOffX = 0;                                    // row tile t: X0 at t*2*kCbOwnBytes, X1 behind it
+constexpr int kCbOffY = 4 * kCbOwnBytes;                      // ring of (Y0, Y1)
 constexpr int kCbOffStat = kCbOffY + kCbStages * 2 * kCbStrBytes;   // ring of 64 x (lse2, delta)
 constexpr int kCbSmemBytes = kCbOffStat + kCbStages * 128 * 4 + 1024;
-// tensor-memory columns (per compute warpgroup w = 0, 1)
-constexpr uint32_t kCbColS = 0, kCbColDP = 128, kCbColP = 256, kCbColDS = 320, kCbColAcc0 = 384, kCbColAcc1 = 448;
+// tensor-memory columns: row tile t holds S at 128 t and dP at 128 t + 64 (P and dS in their first 32
+// columns), its accumulators at 256 + 128 t (dV) and 256 + 128 t + 64 (dK | dQ)
+constexpr uint32_t kCbColBuf = 128, kCbColDP = 64, kCbColAcc = 256, kCbColAcc1 = 64;
 
 struct CbCtl {
   uint64_t x_full, o_full;
   uint64_t y_full[kCbStages], y_empty[kCbStages], st_full[kCbStages];
-  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_full[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
 
 struct CbParams {
   const float *lse, *delta;      // [BH, Nq]
-  __nv_bfloat16 *out0, *out1;    // dK/dV kernel: dV, dK [BH, Nc, 64];  dQ kernel: dQ [BH, Nq, 64], unused
+  __nv_bfloat16 *out0, *out1;    // dK/dV kernel: dV, dK [BH, Nc, 64];  dQ kernel: unused, dQ [BH, Nq, 64]
   int n_own, n_str;              // rows of the owned and of the streamed tensors (Nc, Nq | Nq, Nc)
   int Nq;
   float cs, scale;               // softmax scale * log2(e), softmax scale
@@ -59,9 +64,9 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   __shared__ CbCtl ctl;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int own_tiles = (p.n_own + 127) / 128;
+  const int own_tiles = (p.n_own + kCbOwnRows - 1) / kCbOwnRows;
   const int bh = blockIdx.x / own_tiles;
-  const int r0 = (blockIdx.x % own_tiles) * 128;
+  const int r0 = (blockIdx.x % own_tiles) * kCbOwnRows;
   const int ntiles = (p.n_str + 63) / 64;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
@@ -76,10 +81,9 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
       mbar_init(&ctl.y_empty[s], 1);
       mbar_init(&ctl.st_full[s], 1);
     }
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(&ctl.s_full[w], 1);
-      mbar_init(&ctl.p_full[w], 128);
-      mbar_init(&ctl.pv_done[w], 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&ctl.s_full[t], 1);
+      mbar_init(&ctl.p_full[t], 128);
     }
     mbar_fence_init();
   }
@@ -96,9 +100,12 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&ctl.x_full, 2 * kCbOwnBytes);
-      tma_load_3d(sbase + kCbOffX, &map_x0, &ctl.x_full, 0, r0, bh);
-      tma_load_3d(sbase + kCbOffX + kCbOwnBytes, &map_x1, &ctl.x_full, 0, r0, bh);
+      mbar_expect_tx(&ctl.x_full, 4 * kCbOwnBytes);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        tma_load_3d(sbase + kCbOffX + t * 2 * kCbOwnBytes, &map_x0, &ctl.x_full, 0, r0 + t * 128, bh);
+        tma_load_3d(sbase + kCbOffX + t * 2 * kCbOwnBytes + kCbOwnBytes, &map_x1, &ctl.x_full, 0, r0 + t * 128, bh);
+      }
       int issued = 0;
       for (int i = 0; i < ntiles; ++i) {
         const int s = i % kCbStages;
@@ -117,55 +124,62 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (converged warp, one elected lane issues)
+    {
+      const bool leader = elect_one_sync();
       constexpr uint32_t idesc_1 = umma_idesc_bf16(128, 64, 0, 0);    // both operands K-major
       constexpr uint32_t idesc_2 = umma_idesc_bf16(128, 64, 0, 1);    // B = streamed tile read as [rows][64]: N contiguous
-      auto first = [&](int w, int s) {            // S[w] = X0 Y0^T, dP[w] = X1 Y1^T
-        const uint32_t y = sbase + kCbOffY + s * 2 * kCbStrBytes;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + kCbColS + w * 64, umma_desc_sw128(sbase + kCbOffX + ks * 32), umma_desc_sw128(y + ks * 32), idesc_1, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + kCbColDP + w * 64, umma_desc_sw128(sbase + kCbOffX + kCbOwnBytes + ks * 32),
-                  umma_desc_sw128(y + kCbStrBytes + ks * 32), idesc_1, ks > 0);
+      // descriptors are built once; a tile's descriptor is the base plus its byte offset / 16
+      const uint64_t desc_x = umma_desc_sw128(sbase + kCbOffX), desc_y = umma_desc_sw128(sbase + kCbOffY);
+      auto first = [&](int t, uint64_t y) {       // S[t] = X0[t] Y0^T, dP[t] = X1[t] Y1^T
+        const uint64_t x = desc_x + static_cast<uint64_t>(t * (2 * kCbOwnBytes >> 4));
+        umma_ss_k4<2, 2>(tmem + t * kCbColBuf, x, y, idesc_1, 0u);
+        umma_ss_k4<2, 2>(tmem + t * kCbColBuf + kCbColDP, x + (kCbOwnBytes >> 4), y + (kCbStrBytes >> 4), idesc_1, 0u);
       };
-      auto second = [&](int w, int s, bool acc) {
-        const uint32_t y = sbase + kCbOffY + s * 2 * kCbStrBytes;
-        if (MODE == 0) {                          // dV += P^T dO (Y1),  dK += dS^T Q (Y0)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ts(tmem + kCbColAcc0, tmem + kCbColP + w * 32 + ks * 8, umma_desc_sw128(y + kCbStrBytes + ks * 2048), idesc_2,
-                    (acc || ks > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)            // dK += dS^T Q   |   dQ += dS K      (Y0)
-          umma_ts(tmem + kCbColAcc1, tmem + kCbColDS + w * 32 + ks * 8, umma_desc_sw128(y + ks * 2048), idesc_2,
-                  (acc || ks > 0) ? 1u : 0u);
+      auto second = [&](int t, uint64_t y, uint32_t acc) {
+        const uint32_t d = tmem + kCbColAcc + t * 128;
+        if (MODE == 0)                            // dV += P^T dO (Y1)
+          umma_ts_k4<128>(d, tmem + t * kCbColBuf, y + (kCbStrBytes >> 4), idesc_2, acc);
+        // dK += dS^T Q   |   dQ += dS K      (Y0)
+        umma_ts_k4<128>(d + kCbColAcc1, tmem + t * kCbColBuf + kCbColDP, y, idesc_2, acc);
       };
-      bool ok = mbar_wait(&ctl.x_full, 0, abort_flag);
+      bool ok = mbar_wait_warp(&ctl.x_full, 0, abort_flag);
+      int s_cur = 0, s_prev = 0;                  // ring stages of tiles i and i-1
+      uint32_t ph_cur = 0;
+#pragma unroll 1
       for (int i = 0; i <= ntiles && ok; ++i) {
+        const uint64_t y_cur = desc_y + static_cast<uint64_t>(s_cur * (2 * kCbStrBytes >> 4));
+        const uint64_t y_prev = desc_y + static_cast<uint64_t>(s_prev * (2 * kCbStrBytes >> 4));
         if (i < ntiles) {
-          // S and dP of this warpgroup were last read for tile i-2, whose p_full this thread has waited for
-          const int s = i % kCbStages;
-          ok = mbar_wait(&ctl.y_full[s], (i / kCbStages) & 1, abort_flag);
+          ok = mbar_wait_warp(&ctl.y_full[s_cur], ph_cur, abort_flag);
           if (!ok) break;
-          tc_fence_after();
-          first(i & 1, s);
-          umma_commit(&ctl.s_full[i & 1]);
         }
-        if (i >= 1) {
-          const int k = i - 1, w = k & 1, s = k % kCbStages;
-          ok = mbar_wait(&ctl.p_full[w], (k >> 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          second(w, s, k > 0);
-          umma_commit(&ctl.pv_done[w]);           // P and dS of this warpgroup may be overwritten
-          umma_commit(&ctl.y_empty[s]);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (i >= 1) {
+            ok = mbar_wait_warp(&ctl.p_full[t], (i - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            if (leader) second(t, y_prev, i > 1 ? 1u : 0u);
+          }
+          if (i < ntiles) {
+            // S/dP of this row tile hold P/dS of tile i-1: the MMAs just issued read them first (issue order)
+            tc_fence_after();
+            if (leader) {
+              first(t, y_cur);
+              umma_commit(&ctl.s_full[t]);
+            }
+          }
+          __syncwarp();
         }
+        if (!ok) break;
+        if (i >= 1 && leader) umma_commit(&ctl.y_empty[s_prev]);
+        __syncwarp();
+        s_prev = s_cur;
+        if (++s_cur == kCbStages) { s_cur = 0; ph_cur ^= 1u; }
       }
-      umma_commit(&ctl.o_full);
+      if (leader) umma_commit(&ctl.o_full);
+      __syncwarp();
       if (!ok) {
         volatile uint32_t dummy = 0;
         mbar_wait(&ctl.o_full, 0, &dummy);        // let issued MMAs drain before tensor memory is freed
@@ -192,12 +206,11 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ compute, thread = owned row
-    const int w = (warp - 4) >> 2;
+    const int t = (warp - 4) >> 2;                  // row tile of this warpgroup
     const int quarter = warp & 3;
-    const int row = r0 + quarter * 32 + lane;
+    const int row = r0 + t * 128 + quarter * 32 + lane;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t t_s = lane_base + kCbColS + w * 64, t_dp = lane_base + kCbColDP + w * 64;
-    const uint32_t t_p = lane_base + kCbColP + w * 32, t_ds = lane_base + kCbColDS + w * 32;
+    const uint32_t t_s = lane_base + t * kCbColBuf, t_dp = t_s + kCbColDP;
     const float cs = p.cs;
     float my_lse2 = INFINITY, my_delta = 0.f;       // dQ kernel: this row's statistics
     if (MODE == 1 && row < p.n_own) {
@@ -205,17 +218,11 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
       my_delta = p.delta[static_cast<int64_t>(bh) * p.Nq + row];
     }
     bool ok = true;
-    for (int i = w; i < ntiles; i += 2) {
+    for (int i = 0; i < ntiles; ++i) {
       const int s = i % kCbStages;
-      const uint32_t ph = (i >> 1) & 1;
-      if (!mbar_wait_warp(&ctl.s_full[w], ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&ctl.s_full[t], i & 1, abort_flag)) { ok = false; break; }
       if (MODE == 0 && !mbar_wait_warp(&ctl.st_full[s], (i / kCbStages) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      // P and dS of tile i-2 must have been consumed by their MMAs before they are overwritten
-      if (i >= 2) {
-        if (!mbar_wait_warp(&ctl.pv_done[w], ph ^ 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-      }
       const float4* st4 = reinterpret_cast<const float4*>(stats + s * 128);
       auto process = [&](uint32_t (&xs)[16], uint32_t (&xd)[16], int c) {
         uint32_t pk[8], dk[8];
@@ -241,8 +248,9 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
           dk[2 * g4] = pack_bf16(dv[0], dv[1]);
           dk[2 * g4 + 1] = pack_bf16(dv[2], dv[3]);
         }
-        if (MODE == 0) tmem_st8(t_p + c * 8, pk);
-        tmem_st8(t_ds + c * 8, dk);
+        // in place: columns 8c..8c+7 of S / dP were read with chunk c/2
+        if (MODE == 0) tmem_st8(t_s + c * 8, pk);
+        tmem_st8(t_dp + c * 8, dk);
       };
       // tensor-memory loads run one chunk ahead of the arithmetic
       uint32_t sa[16], da[16], sb[16], db[16];
@@ -263,21 +271,20 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&ctl.p_full[w]);
+      mbar_arrive(&ctl.p_full[t]);
     }
-    // epilogue: the accumulators -> bf16.  dK/dV kernel: warpgroup 0 stores dV, warpgroup 1 dK (scaled);
-    // dQ kernel: each warpgroup stores one half of dQ's channels (scaled).
+    // epilogue: this row tile's accumulators -> bf16 (dK and dQ carry the softmax scale)
     if (ok) ok = mbar_wait_warp(&ctl.o_full, 0, abort_flag);
     if (ok) {
       tc_fence_after();
-      if (MODE == 0) {
-        const uint32_t t_acc = lane_base + (w == 0 ? kCbColAcc0 : kCbColAcc1);
-        const float f = (w == 0) ? 1.f : p.scale;
-        __nv_bfloat16* out = (w == 0 ? p.out0 : p.out1) + (static_cast<int64_t>(bh) * p.n_own + row) * 64;
+#pragma unroll 1
+      for (int a = (MODE == 0 ? 0 : 1); a < 2; ++a) {
+        const float f = (a == 0) ? 1.f : p.scale;
+        __nv_bfloat16* out = (a == 0 ? p.out0 : p.out1) + (static_cast<int64_t>(bh) * p.n_own + row) * 64;
 #pragma unroll 1
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t o[32];
-          tmem_ld32(t_acc + hf * 32, o);
+          tmem_ld32(lane_base + kCbColAcc + t * 128 + a * kCbColAcc1 + hf * 32, o);
           tmem_ld_wait();
           if (row < p.n_own) {
             uint4* dst = reinterpret_cast<uint4*>(out + hf * 32);
@@ -288,20 +295,6 @@ cmp_bwd_kernel(const __grid_constant__ CUtensorMap map_x0, const __grid_constant
                                   pack_bf16(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f),
                                   pack_bf16(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f));
           }
-        }
-      } else {
-        uint32_t o[32];
-        tmem_ld32(lane_base + kCbColAcc1 + w * 32, o);
-        tmem_ld_wait();
-        if (row < p.n_own) {
-          const float f = p.scale;
-          uint4* dst = reinterpret_cast<uint4*>(p.out0 + (static_cast<int64_t>(bh) * p.n_own + row) * 64 + w * 32);
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            dst[v] = make_uint4(pack_bf16(__uint_as_float(o[8 * v]) * f, __uint_as_float(o[8 * v + 1]) * f),
-                                pack_bf16(__uint_as_float(o[8 * v + 2]) * f, __uint_as_float(o[8 * v + 3]) * f),
-                                pack_bf16(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f),
-                                pack_bf16(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f));
         }
       }
     }
@@ -364,12 +357,13 @@ extern "C" int s3r_cmp_attn_bwd(const void* q_c, const void* k_c, const void* v_
   p.out0 = static_cast<__nv_bfloat16*>(dv_c);
   p.out1 = static_cast<__nv_bfloat16*>(dk_c);
   p.n_own = Nc; p.n_str = Nq;
-  const int64_t g0 = static_cast<int64_t>(BH) * ((Nc + 127) / 128), g1 = static_cast<int64_t>(BH) * ((Nq + 127) / 128);
+  const int64_t g0 = static_cast<int64_t>(BH) * ((Nc + kCbOwnRows - 1) / kCbOwnRows),
+                g1 = static_cast<int64_t>(BH) * ((Nq + kCbOwnRows - 1) / kCbOwnRows);
   S3R_REQUIRE(g0 < (1ll << 31) && g1 < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_cmp_attn_bwd: grid too large");
   cmp_bwd_kernel<0><<<static_cast<unsigned>(g0), kCbThreads, kCbSmemBytes, st>>>(mk128, mv128, mq64, mdo64, p);
   // dQ: own = Q, dO (Nq rows), streamed = K, V (Nc rows)
-  p.out0 = static_cast<__nv_bfloat16*>(dq_c);
-  p.out1 = nullptr;
+  p.out0 = nullptr;
+  p.out1 = static_cast<__nv_bfloat16*>(dq_c);
   p.n_own = Nq; p.n_str = Nc;
   cmp_bwd_kernel<1><<<static_cast<unsigned>(g1), kCbThreads, kCbSmemBytes, st>>>(mq128, mdo128, mk64, mv64, p);
   S3R_CUDA(cudaGetLastError());
