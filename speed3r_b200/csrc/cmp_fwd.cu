@@ -235,63 +235,81 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (converged warp, one elected lane issues)
+    {
+      const bool leader = elect_one_sync();
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 0, 1);   // V tile is [keys][d]: N contiguous
+      // descriptors are built once; a tile's descriptor is the base plus its byte offset / 16
+      const uint64_t desc_q = umma_desc_sw128(sbase + kOffQ), desc_k = umma_desc_sw128(sbase + kOffK),
+                     desc_v = umma_desc_sw128(sbase + kOffV);
       auto issue_qk = [&](int t, int s) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + kColS + t * 128, umma_desc_sw128(sbase + kOffQ + t * kTileBytes + ks * 32),
-                  umma_desc_sw128(sbase + kOffK + s * kTileBytes + ks * 32), idesc_qk, ks > 0);
+        umma_ss_k4<2, 2>(tmem + kColS + t * 128, desc_q + static_cast<uint64_t>(t * (kTileBytes >> 4)),
+                         desc_k + static_cast<uint64_t>(s * (kTileBytes >> 4)), idesc_qk, 0u);
       };
-      auto issue_pv = [&](int t, int s, bool acc) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tmem + kColO + t * 64, tmem + kColP + t * 64 + ks * 8,
-                  umma_desc_sw128(sbase + kOffV + s * kTileBytes + ks * 2048), idesc_pv, (acc || ks > 0) ? 1u : 0u);
+      auto issue_pv = [&](int t, int s, uint32_t acc) {
+        const uint64_t v = desc_v + static_cast<uint64_t>(s * (kTileBytes >> 4));
+        umma_ts_k4<128>(tmem + kColO + t * 64, tmem + kColP + t * 64, v, idesc_pv, acc);
+        umma_ts_k4<128>(tmem + kColO + t * 64, tmem + kColP + t * 64 + 32, v + 4 * 128, idesc_pv, 1u);
       };
-      bool ok = mbar_wait(&ctl.q_full, 0, abort_flag) && mbar_wait(&ctl.k_full[0], 0, abort_flag);
+      bool ok = mbar_wait_warp(&ctl.q_full, 0, abort_flag) && mbar_wait_warp(&ctl.k_full[0], 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_qk(0, 0);
-        umma_commit(&ctl.s_full[0]);
-        issue_qk(1, 0);
-        umma_commit(&ctl.s_full[1]);
-        umma_commit(&ctl.k_empty[0]);
+        if (leader) {
+          issue_qk(0, 0);
+          umma_commit(&ctl.s_full[0]);
+          issue_qk(1, 0);
+          umma_commit(&ctl.s_full[1]);
+          umma_commit(&ctl.k_empty[0]);
+        }
+        __syncwarp();
+        int s = 0, sn = 1 % kStages;
+        uint32_t ph = 0, phn = (1 / kStages) & 1;
+#pragma unroll 1
         for (int j = 0; j < ntiles && ok; ++j) {
-          const int s = j % kStages;
           const bool nxt = j + 1 < ntiles;
-          const int sn = (j + 1) % kStages;
-          ok = mbar_wait(&ctl.v_full[s], (j / kStages) & 1, abort_flag);
-          if (ok && nxt) ok = mbar_wait(&ctl.k_full[sn], ((j + 1) / kStages) & 1, abort_flag);
-          for (int t = 0; t < 2 && ok; ++t) {
-            ok = mbar_wait(&ctl.p_full[t], j & 1, abort_flag);
+          ok = mbar_wait_warp(&ctl.v_full[s], ph, abort_flag);
+          if (ok && nxt) ok = mbar_wait_warp(&ctl.k_full[sn], phn, abort_flag);
+          if (!ok) break;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            ok = mbar_wait_warp(&ctl.p_full[t], j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             // The next scores are what the 256 waiting threads need; P V only has to finish before the next
             // P V of the tile.  So when the top-k warps have released S already, Q K^T goes first.
-            const bool qk_first = nxt && mbar_test_wait(&ctl.tk_done[t], j & 1);
+            const bool qk_first = nxt && __all_sync(0xffffffffu, mbar_test_wait(&ctl.tk_done[t], j & 1));
             if (qk_first) {
               tc_fence_after();
-              issue_qk(t, sn);
-              umma_commit(&ctl.s_full[t]);
+              if (leader) {
+                issue_qk(t, sn);
+                umma_commit(&ctl.s_full[t]);
+              }
             }
-            issue_pv(t, s, j > 0);
-            umma_commit(&ctl.pv_done[t]);          // P of this tile may be overwritten, O is at rest
-            if (t == 1) umma_commit(&ctl.v_empty[s]);
+            if (leader) {
+              issue_pv(t, s, j > 0 ? 1u : 0u);
+              umma_commit(&ctl.pv_done[t]);          // P of this tile may be overwritten, O is at rest
+              if (t == 1) umma_commit(&ctl.v_empty[s]);
+            }
+            __syncwarp();
             if (nxt && !qk_first) {
-              ok = mbar_wait(&ctl.tk_done[t], j & 1, abort_flag);    // S of this tile has been read by top-k too
+              ok = mbar_wait_warp(&ctl.tk_done[t], j & 1, abort_flag);    // S of this tile has been read by top-k too
               if (!ok) break;
               tc_fence_after();
-              issue_qk(t, sn);
-              umma_commit(&ctl.s_full[t]);
+              if (leader) {
+                issue_qk(t, sn);
+                umma_commit(&ctl.s_full[t]);
+              }
             }
-            if (nxt && t == 1) umma_commit(&ctl.k_empty[sn]);
+            if (nxt && t == 1 && leader) umma_commit(&ctl.k_empty[sn]);
+            __syncwarp();
           }
+          s = sn; ph = phn;
+          if (++sn == kStages) { sn = 0; phn ^= 1u; }
         }
       }
-      umma_commit(&ctl.o_full);
+      if (leader) umma_commit(&ctl.o_full);
+      __syncwarp();
       if (!ok) {
         volatile uint32_t dummy = 0;
         mbar_wait(&ctl.o_full, 0, &dummy);     // let issued MMAs drain before tensor memory is freed

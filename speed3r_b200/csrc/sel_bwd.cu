@@ -399,9 +399,16 @@ __global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dq_kernel(const SelBwd
   store_acc_bf16(dq, [&](int r) { return (row0 + r < p.Tq) ? out + r * 64 : nullptr; }, lane);
 }
 
+// The loop over the query blocks that selected this key block is a chain of dependent accesses (list
+// entry -> row addresses -> rows and their lse/delta), so everything is fetched ahead: the list 32 entries
+// at a time into a register per lane (read back with a shuffle), rows and statistics by cp.async into a
+// ring kDkdvStages deep.  Nothing in the loop waits for a load it has just issued.
+constexpr int kDkdvStages = 3;
+constexpr int kDkdvStageBytes = 2 * kTile + 128;          // Q tile, dO tile, 16 x lse | 16 x delta
+constexpr int kDkdvSmemBytes = kBwdWarps * kDkdvStages * kDkdvStageBytes;
+
 __global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dkdv_kernel(const SelBwdParams p) {
-  __shared__ __align__(16) uint8_t smem[kBwdWarps][2][2 * kTile];
-  __shared__ float stats[kBwdWarps][2][32];           // [stage][lse2 x16 | delta x16]
+  extern __shared__ __align__(16) uint8_t dkdv_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nslices = (p.Tk + 15) / 16;
   const int64_t task = static_cast<int64_t>(blockIdx.x) * kBwdWarps + warp;
@@ -409,7 +416,8 @@ __global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dkdv_kernel(const SelB
   const int bh = static_cast<int>(task / nslices);
   const int row0 = static_cast<int>(task % nslices) * 16;
   const int n = row0 / p.block;
-  const uint32_t sm0 = smem_u32(&smem[warp][0][0]), sm1 = smem_u32(&smem[warp][1][0]);
+  uint8_t* my = dkdv_smem + warp * kDkdvStages * kDkdvStageBytes;
+  const uint32_t sm0 = smem_u32(my);
 
   uint32_t kf[4][4], vf[4][4];
   const int krows = min(16, p.Tk - row0);
@@ -433,31 +441,46 @@ __global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dkdv_kernel(const SelB
   float dk[8][4] = {}, dv[8][4] = {};
   const int spb = p.block / 16;
   const int ntiles = cnt * spb;
+  // list entries of chunk c (32 of them) live in `q_cur`, those of chunk c+1 in `q_nxt`
+  int q_chunk = 0;
+  int q_cur = (lane < cnt) ? ql[lane] : 0;
+  int q_nxt = (32 + lane < cnt) ? ql[32 + lane] : 0;
   auto prefetch = [&](int it) {
-    const int tok0 = ql[it / spb] * p.block + (it % spb) * 16;
-    const uint32_t dst = (it & 1) ? sm1 : sm0;
+    const int qb = it / spb;
+    if ((qb >> 5) != q_chunk) {                       // warp-uniform
+      q_chunk = qb >> 5;
+      q_cur = q_nxt;
+      const int j = (q_chunk + 1) * 32 + lane;
+      q_nxt = (j < cnt) ? ql[j] : 0;
+    }
+    const int tok0 = __shfl_sync(0xffffffffu, q_cur, qb & 31) * p.block + (it % spb) * 16;
+    const uint32_t dst = sm0 + (it % kDkdvStages) * kDkdvStageBytes;
     const int nrows = max(0, min(16, p.Tq - tok0));
     load_tile16(dst, Qb + static_cast<int64_t>(tok0) * 64, nrows, lane);
     load_tile16(dst + kTile, Db + static_cast<int64_t>(tok0) * 64, nrows, lane);
-    cp_async_commit();
-    // per-query statistics: lanes 0-15 lse, lanes 16-31 delta
+    // per-query statistics: lanes 0-15 lse, lanes 16-31 delta (a padding query gets 0 and 0: its Q and dO
+    // rows are zero as well, so P = 1 meets dO = 0 and dP - delta = 0)
     const int t = tok0 + (lane & 15);
-    float val;
-    if (lane < 16) {
-      float l = (t < p.Tq) ? Lb[t] : INFINITY;
-      if (l == -INFINITY) l = INFINITY;
-      val = l * 1.4426950408889634f;
-    } else {
-      val = (t < p.Tq) ? Eb[t] : 0.f;
-    }
-    stats[warp][it & 1][lane] = val;
+    cp_async4(dst + 2 * kTile + lane * 4, (lane < 16 ? Lb : Eb) + min(t, p.Tq - 1), t < p.Tq);
+    cp_async_commit();
   };
-  if (ntiles > 0) prefetch(0);
+#pragma unroll
+  for (int a = 0; a < kDkdvStages - 1; ++a) {
+    if (a < ntiles) prefetch(a); else cp_async_commit();
+  }
   for (int it = 0; it < ntiles; ++it) {
-    if (it + 1 < ntiles) { prefetch(it + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    if (it + kDkdvStages - 1 < ntiles) prefetch(it + kDkdvStages - 1); else cp_async_commit();
+    cp_async_wait<kDkdvStages - 1>();
     __syncwarp();
-    const uint32_t cur = (it & 1) ? sm1 : sm0;
-    pair_dkdv(kf, vf, cur, cur + kTile, &stats[warp][it & 1][0], &stats[warp][it & 1][16], p.cs, p.scale, dk, dv, lane);
+    uint8_t* st = my + (it % kDkdvStages) * kDkdvStageBytes;
+    float* stats = reinterpret_cast<float*>(st + 2 * kTile);
+    if (lane < 16) {                                  // lse -> lse * log2(e); a row without any valid key: no gradient
+      const float l = stats[lane];
+      stats[lane] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+    }
+    __syncwarp();
+    const uint32_t cur = smem_u32(st);
+    pair_dkdv(kf, vf, cur, cur + kTile, stats, stats + 16, p.cs, p.scale, dk, dv, lane);
     __syncwarp();
   }
   __nv_bfloat16* okp = p.dk + (static_cast<int64_t>(bh) * p.Tk + row0) * 64;
@@ -627,7 +650,8 @@ extern "C" int s3r_sel_attn_bwd(const void* q, const void* k, const void* v, con
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t bh = static_cast<int64_t>(B) * H;
   const int64_t tq = bh * ((Tq + 15) / 16), tk = bh * ((Tk + 15) / 16);
-  sel_bwd_dkdv_kernel<<<static_cast<unsigned>((tk + kBwdWarps - 1) / kBwdWarps), kBwdWarps * 32, 0, st>>>(p);
+  S3R_CUDA(cudaFuncSetAttribute(sel_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkdvSmemBytes));
+  sel_bwd_dkdv_kernel<<<static_cast<unsigned>((tk + kBwdWarps - 1) / kBwdWarps), kBwdWarps * 32, kDkdvSmemBytes, st>>>(p);
   sel_bwd_dq_kernel<<<static_cast<unsigned>((tq + kBwdWarps - 1) / kBwdWarps), kBwdWarps * 32, 0, st>>>(p);
   S3R_CUDA(cudaGetLastError());
   return 0;
