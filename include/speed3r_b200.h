@@ -174,7 +174,10 @@ int s3r_build_key_csr(const int32_t* idx, int32_t* offsets, int32_t* qids, int B
  *   - Tables whose scratch (s3r_csr_workspace_bytes) exceeds the buffer are refused with
  *     S3R_ERR_TOO_LARGE and a message; nothing is launched.
  *   - The first call on each device resolves the buffer's device address (cudaGetSymbolAddress
- *     with that device current).  Make that first call during set-up, before any stream capture.
+ *     with that device current); under lazy module loading that may load the library's device
+ *     code then, which synchronises.  Make that first call during set-up.  The address is cached
+ *     per device ordinal and is valid for the life of that device's primary context.
+ *   - The buffer is 256-byte aligned, as the workspace of s3r_build_key_csr has to be.
  *   - All calls on a device share the one buffer, which keeps whatever the previous call left; the
  *     kernels overwrite every slot they later read, so nothing needs clearing.  Two calls that
  *     overlap on the GPU (different streams) race on it: serialise them.

@@ -6,7 +6,8 @@
 // the top-k threshold tests as the practical co-limit.  The MMAs are taken off the issue path and
 // the two per-element jobs run on different warps so that their latencies overlap:
 //   warp 0  (1 lane)   TMA producer: Q tile pair once, then K and V tiles of 128 keys into rings
-//   warp 1  (1 lane)   tcgen05.mma issuer: S = Q K^T (M=128,N=128) and O += P V (M=128,N=64)
+//   warp 1             tcgen05.mma issuer (converged warp, one elected lane issues): S = Q K^T (M=128,N=128)
+//                      and O += P V (M=128,N=64)
 //   warp 2             tensor-memory allocator
 //   warps 4-7, 8-11    softmax warpgroups, one per 128-row query tile; thread = row
 //   warps 12-15, 16-19 top-k warpgroups, one per query tile; thread = row, reading the same S
