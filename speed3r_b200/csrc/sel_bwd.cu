@@ -324,7 +324,10 @@ __device__ __forceinline__ void load_tile16(uint32_t dst, const __nv_bfloat16* s
   }
 }
 
-__global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dq_kernel(const SelBwdParams p) {
+#ifndef S3R_DQ_MIN_CTAS
+#define S3R_DQ_MIN_CTAS 1
+#endif
+__global__ void __launch_bounds__(kBwdWarps * 32, S3R_DQ_MIN_CTAS) sel_bwd_dq_kernel(const SelBwdParams p) {
   __shared__ __align__(16) uint8_t smem[kBwdWarps][2][2 * kTile];
   __shared__ int32_t lists[kBwdWarps][64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -403,15 +406,28 @@ __global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dq_kernel(const SelBwd
 // entry -> row addresses -> rows and their lse/delta), so everything is fetched ahead: the list 32 entries
 // at a time into a register per lane (read back with a shuffle), rows and statistics by cp.async into a
 // ring kDkdvStages deep.  Nothing in the loop waits for a load it has just issued.
-constexpr int kDkdvStages = 3;
+// One warp per CTA: the loop length of a warp is the number of query blocks that selected its key block,
+// which varies from warp to warp; warps sharing a CTA would hold its registers and shared memory until the
+// longest of them is done.
+#ifndef S3R_DKDV_WARPS
+#define S3R_DKDV_WARPS 1
+#endif
+#ifndef S3R_DKDV_MIN_CTAS
+#define S3R_DKDV_MIN_CTAS 16               // caps the kernel at 128 registers: 16 instead of 10 warps per SM
+#endif
+#ifndef S3R_DKDV_STAGES
+#define S3R_DKDV_STAGES 3
+#endif
+constexpr int kDkdvWarps = S3R_DKDV_WARPS;
+constexpr int kDkdvStages = S3R_DKDV_STAGES;
 constexpr int kDkdvStageBytes = 2 * kTile + 128;          // Q tile, dO tile, 16 x lse | 16 x delta
-constexpr int kDkdvSmemBytes = kBwdWarps * kDkdvStages * kDkdvStageBytes;
+constexpr int kDkdvSmemBytes = kDkdvWarps * kDkdvStages * kDkdvStageBytes;
 
-__global__ void __launch_bounds__(kBwdWarps * 32) sel_bwd_dkdv_kernel(const SelBwdParams p) {
+__global__ void __launch_bounds__(kDkdvWarps * 32, S3R_DKDV_MIN_CTAS) sel_bwd_dkdv_kernel(const SelBwdParams p) {
   extern __shared__ __align__(16) uint8_t dkdv_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nslices = (p.Tk + 15) / 16;
-  const int64_t task = static_cast<int64_t>(blockIdx.x) * kBwdWarps + warp;
+  const int64_t task = static_cast<int64_t>(blockIdx.x) * kDkdvWarps + warp;
   if (task >= static_cast<int64_t>(p.B) * p.H * nslices) return;
   const int bh = static_cast<int>(task / nslices);
   const int row0 = static_cast<int>(task % nslices) * 16;
@@ -651,7 +667,8 @@ extern "C" int s3r_sel_attn_bwd(const void* q, const void* k, const void* v, con
   const int64_t bh = static_cast<int64_t>(B) * H;
   const int64_t tq = bh * ((Tq + 15) / 16), tk = bh * ((Tk + 15) / 16);
   S3R_CUDA(cudaFuncSetAttribute(sel_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkdvSmemBytes));
-  sel_bwd_dkdv_kernel<<<static_cast<unsigned>((tk + kBwdWarps - 1) / kBwdWarps), kBwdWarps * 32, kDkdvSmemBytes, st>>>(p);
+  S3R_REQUIRE((tk + kDkdvWarps - 1) / kDkdvWarps < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_sel_attn_bwd: grid too large");
+  sel_bwd_dkdv_kernel<<<static_cast<unsigned>((tk + kDkdvWarps - 1) / kDkdvWarps), kDkdvWarps * 32, kDkdvSmemBytes, st>>>(p);
   sel_bwd_dq_kernel<<<static_cast<unsigned>((tq + kBwdWarps - 1) / kBwdWarps), kBwdWarps * 32, 0, st>>>(p);
   S3R_CUDA(cudaGetLastError());
   return 0;
