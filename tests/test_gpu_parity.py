@@ -173,6 +173,31 @@ def test_sel_attn_seeded_fwd_bwd(B, H, T, Bs, K):
     assert_bf16_close(vg.grad, vr.grad, "dv")
 
 
+def test_sel_attn_backward_sink_blocks():
+    """Key blocks that every query block selects (long CSR segments: the register-chunked list walk of the
+    dK/dV kernel crosses many 32-entry chunks) next to blocks nobody selects (empty segments)."""
+    from speed3r_b200 import ops
+    B, H, T, Bs, K = 1, 2, 3200, 16, 8
+    q, k, v = bf16_round(randn(41, B, H, T, 64), randn(42, B, H, T, 64), randn(43, B, H, T, 64))
+    nb = T // Bs                                  # 200 query blocks
+    idx = _rand_idx(44, B, H, nb, nb // 2, K)     # the upper half of the key blocks is never selected ...
+    idx[:, :, :, 0] = 0                           # ... block 0 by every query block
+    idx[:, :, :, 1] = 7                           # and block 7 as well
+    idx[:, :, ::3, 2] = nb - 1                    # every third one the last block
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    o_ref, _ = R.sel_attn(qr, kr, vr, idx, Bs)
+    qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
+    o = ops.topk_blocksparse_attention(qg, kg, vg, idx.to(DEV), Bs)
+    assert_bf16_close(o, o_ref, "o_s")
+    do, = bf16_round(randn(45, B, H, T, 64))
+    o_ref.backward(do)
+    o.backward(dev(do))
+    assert_bf16_close(qg.grad, qr.grad, "dq")
+    assert_bf16_close(kg.grad, kr.grad, "dk")
+    assert_bf16_close(vg.grad, vr.grad, "dv")
+    assert float(kg.grad[:, :, (nb // 2 + 1) * Bs:(nb - 1) * Bs].abs().max()) == 0.0   # unselected blocks: exact zeros
+
+
 def test_sel_attn_merge_fused_fwd_bwd():
     from speed3r_b200 import ops
     B, H, T, Bs, K = 2, 4, 656, 16, 32
