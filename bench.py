@@ -450,8 +450,7 @@ def main():
         q, k, v, gate = qg, kg, vg, gateg
     g = torch.Generator(device=dev).manual_seed(99)
     bwd = args.mode == "fwdbwd"
-    if bwd and world > 1:
-        raise SystemExit("fwdbwd is single-GPU in this benchmark")
+    # fwdbwd at N > 1: the differentiable partitioned op (dense gathered K/V; dK/dV reduce-scattered in the backward)
     dy = torch.randn(1, Tl, H * D, device=dev, generator=g).bfloat16() if bwd else None
     # high priority: the all-gather's few CTAs must not queue behind the compression kernel, which fills every SM
     side = torch.cuda.Stream(priority=-1) if world > 1 else None
@@ -488,6 +487,12 @@ def main():
 
     def step(record=False):
         """Returns y; with record=True also appends per-kernel CUDA events."""
+        if world > 1 and bwd:
+            ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+            y, _ = seq_parallel.sparse_attention_partitioned_grad(ql, kl, vl, gate, BS, TOPK, ops.pool_tokens,
+                                                                  ops.flash_attn_topk_func, ops.sel_attn_merge)
+            y.backward(dy)
+            return y
         if world > 1:
             return step_partitioned(q, k, v, gate, record)
         if bwd:

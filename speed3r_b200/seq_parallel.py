@@ -217,12 +217,57 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
     return y, idx
 
 
+class _GatherSeq(torch.autograd.Function):
+    """All-gather of ``x [B,H,n,d]`` along the sequence into ``[B,H,G*n,d]`` (rank order = sequence order).
+    Its backward is the matching reduce-scatter: every rank holds gradient contributions to ALL tokens (from
+    its own queries) and receives the sum over ranks of the contributions to its own tokens."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        ctx.group = group
+        return chunks_to_dense(all_gather_chunks(x.contiguous(), group))
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        world = dist.get_world_size(ctx.group)
+        B, H, T, d = g.shape
+        n = T // world
+        chunks = g.reshape(B, H, world, n, d).permute(2, 0, 1, 3, 4).contiguous()      # [G,B,H,n,d]
+        if dist.get_backend(ctx.group) == "gloo":            # no reduce-scatter there: reduce, keep the own chunk
+            dist.all_reduce(chunks, group=ctx.group)
+            return chunks[dist.get_rank(ctx.group)].clone(), None
+        out = torch.empty_like(chunks[0])
+        dist.reduce_scatter_tensor(out, chunks, group=ctx.group)
+        return out, None
+
+
+def sparse_attention_partitioned_grad(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, block: int, topk: int,
+                                      pool: Callable, cmp_attn_topk: Callable, sel_attn_merge: Callable,
+                                      group=None, pooled: Optional[Tuple[Tensor, Tensor, Tensor]] = None):
+    """The differentiable form of ``sparse_attention_partitioned`` (training on sequences longer than one
+    GPU holds): same arguments, but ``cmp_attn_topk`` and ``sel_attn_merge`` are the differentiable ops and
+    take K/V as dense ``[B,H,T,d]`` tensors.  Gradients with respect to this rank's ``q`` and ``gate`` are
+    local; those with respect to ``k``, ``v`` (and the pooled ``k_c``, ``v_c``) are computed by every rank for
+    all keys from its own queries and reduce-scattered by the backward of the all-gathers.  The partial
+    gradients are rounded to the tensors' dtype before the reduction, so the result differs from the
+    single-GPU gradient by that rounding (it is not bit-equal as the forward is)."""
+    if pooled is None:
+        pooled = (pool(q, block, block), pool(k, block, block), pool(v, block, block))
+    q_c, k_c, v_c = pooled
+    kc_all, vc_all = _GatherSeq.apply(k_c, group), _GatherSeq.apply(v_c, group)
+    k_all, v_all = _GatherSeq.apply(k, group), _GatherSeq.apply(v, group)
+    o_c, idx = cmp_attn_topk(q_c, kc_all, vc_all, topk)
+    y = sel_attn_merge(q, k_all, v_all, idx, gate, o_c, block)
+    return y, idx
+
+
 class SequenceParallel:
     """What the drop-in module needs to run its two attention branches sequence-partitioned: set
     ``module.seq_parallel = SequenceParallel(group)`` on every global-attention module of a model whose
     ranks each hold a contiguous slice of the views (token order is view-major).  The module's own
-    prologue (split, LayerNorm, rotary embedding, pooling) stays local; this object does the exchange.
-    Forward only (inference)."""
+    prologue (split, LayerNorm, rotary embedding, pooling) stays local; this object does the exchange:
+    ``attention`` for inference (chunked K/V, exchange overlapped with the compression kernel),
+    ``attention_grad`` when gradients are needed (dense K/V, reduce-scatter of dK/dV in the backward)."""
 
     def __init__(self, group=None, gather: str = "nccl"):
         self.group = group
@@ -247,3 +292,8 @@ class SequenceParallel:
             kw.update(side_stream=self._side, side_group=self._side_group)
         return sparse_attention_partitioned(q, k, v, gate, block, topk, None, cmp_attn_topk, sel_attn_merge,
                                             group=self.group, pooled=(q_c, k_c, v_c), **kw)
+
+    def attention_grad(self, q: Tensor, k: Tensor, v: Tensor, q_c: Tensor, k_c: Tensor, v_c: Tensor, gate: Tensor,
+                       block: int, topk: int, cmp_attn_topk: Callable, sel_attn_merge: Callable):
+        return sparse_attention_partitioned_grad(q, k, v, gate, block, topk, None, cmp_attn_topk, sel_attn_merge,
+                                                 group=self.group, pooled=(q_c, k_c, v_c))

@@ -203,9 +203,8 @@ class SparseFlashAttentionRope(nn.Module):
         gate = gate.to(qkv.dtype)
         if self._can_fuse_prologue(qkv, x, xpos, N, Bs, d):
             return self._forward_fused(qkv, gate, xpos, B, N, H, d, Bs)
-        if self.seq_parallel is not None:
-            raise RuntimeError("sequence-parallel attention is inference-only: run under torch.no_grad() with "
-                               "LayerNorm q/k norms, a 2-D rotary module and whole 16-token blocks")
+        if self.seq_parallel is not None and N % Bs != 0:
+            raise RuntimeError("sequence-parallel attention needs whole 16-token blocks on every rank")
         qkv5 = qkv.view(B, N, 3, H, d)
         q_t, k_t, v_t = (qkv5[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # [B,H,N,d] views of the projection
 
@@ -219,15 +218,19 @@ class SparseFlashAttentionRope(nn.Module):
             xpos_c = xpos.view(B, N // Bs, Bs, 2).float().mean(dim=2).int()
             q_c = self.rope(q_c, xpos_c, **rope_kw)
             k_c = self.rope(k_c, xpos_c, **rope_kw)
-        o_c, idx = ops.flash_attn_topk_func(q_c, k_c, v_c, self.topk)
-        if self.record_idx:
-            self.last_idx = idx.detach()
-
         # selection branch at token level, gated merge fused into its epilogue
         q, k = self.q_norm(q_t).to(qkv.dtype), self.k_norm(k_t).to(qkv.dtype)
         if xpos is not None:
             q = self.rope(q, xpos, **rope_kw)
             k = self.rope(k, xpos, **rope_kw)
-        y = ops.sel_attn_merge(q.contiguous(), k.contiguous(), v_t.contiguous(), idx, gate, o_c, Bs)
+        if self.seq_parallel is not None:
+            # this rank's queries against the whole sequence; the backward reduce-scatters dK and dV
+            y, idx = self.seq_parallel.attention_grad(q.contiguous(), k.contiguous(), v_t.contiguous(), q_c, k_c, v_c,
+                                                      gate, Bs, self.topk, ops.flash_attn_topk_func, ops.sel_attn_merge)
+        else:
+            o_c, idx = ops.flash_attn_topk_func(q_c, k_c, v_c, self.topk)
+            y = ops.sel_attn_merge(q.contiguous(), k.contiguous(), v_t.contiguous(), idx, gate, o_c, Bs)
+        if self.record_idx:
+            self.last_idx = idx.detach()
         y = self.proj(y)
         return self.proj_drop(y)

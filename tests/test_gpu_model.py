@@ -266,3 +266,138 @@ def test_partitioned_op_equals_single_gpu(use_side):
         pr.join(300)
     assert all(pr.exitcode == 0 for pr in procs), [pr.exitcode for pr in procs]
     assert result.get(timeout=5) is True
+
+
+def _partition_grad_worker(rank, world, port, views, result):
+    import torch.distributed as dist
+    from speed3r_b200 import ops, seq_parallel
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        H, D, BS, K = 4, 64, 16, 32
+        T = views * 1008
+        g = torch.Generator(device=dev).manual_seed(78)
+        ln = lambda t: torch.nn.functional.layer_norm(t, (D,))
+        q, k, v = (ln(torch.randn(1, H, T, D, device=dev, generator=g)).bfloat16() for _ in range(3))
+        gate = torch.sigmoid(torch.randn(1, H, T, 2, device=dev, generator=g)).bfloat16()
+        dy = torch.randn(1, T, H * D, device=dev, generator=g).bfloat16()
+        t0, t1 = seq_parallel.partition(T, BS, world, rank)
+        ql, kl, vl, gl = (t[:, :, t0:t1].contiguous().requires_grad_(True) for t in (q, k, v, gate))
+        y, idx = seq_parallel.sparse_attention_partitioned_grad(ql, kl, vl, gl, BS, K, ops.pool_tokens,
+                                                                ops.flash_attn_topk_func, ops.sel_attn_merge)
+        y.backward(dy[:, t0:t1].contiguous())
+        qf, kf, vf, gf = (t.clone().requires_grad_(True) for t in (q, k, v, gate))
+        qc, kc, vc = (ops.pool_tokens(t, BS, BS) for t in (qf, kf, vf))
+        o_c, idx_f = ops.flash_attn_topk_func(qc, kc, vc, K)
+        y_f = ops.sel_attn_merge(qf, kf, vf, idx_f, gf, o_c, BS)
+        y_f.backward(dy)
+        torch.cuda.synchronize()
+        ok = torch.equal(y.detach(), y_f.detach()[:, t0:t1]) and torch.equal(idx, idx_f[:, :, t0 // BS:t1 // BS])
+        # dq, dgate: the same kernels on the same rows; dk, dv: partial sums rounded to bf16 before the reduction
+        for name, a, b, tol in (("dq", ql.grad, qf.grad[:, :, t0:t1], 0.0), ("dgate", gl.grad, gf.grad[:, :, t0:t1], 0.0),
+                                ("dk", kl.grad, kf.grad[:, :, t0:t1], 3e-2), ("dv", vl.grad, vf.grad[:, :, t0:t1], 3e-2)):
+            diff = (a.float() - b.float()).abs().max().item()
+            scale = max(1.0, b.float().abs().max().item())
+            if diff > tol * scale:
+                print(f"rank {rank}: {name} differs by {diff} (scale {scale})", flush=True)
+                ok = False
+        flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            result.put(bool(flag.item() == 1.0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_partitioned_op_gradients_match_single_gpu():
+    """Forward + backward of the sequence-partitioned op on 2+ GPUs against the single-GPU op on the global
+    tensors: outputs, tables, dQ and dgate bit-equal; dK and dV (reduce-scattered bf16 partial sums) within
+    bf16 rounding of the single-GPU gradients."""
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    while (20 * 1008) % (16 * world):
+        world -= 1
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = 29500 + (os.getpid() % 500) + 7
+    procs = [ctx.Process(target=_partition_grad_worker, args=(r, world, port, 20, result)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(300)
+    assert all(pr.exitcode == 0 for pr in procs), [pr.exitcode for pr in procs]
+    assert result.get(timeout=5) is True
+
+
+def _ddp_worker(rank, world, port, result):
+    import torch.distributed as dist
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    import speed3r_b200
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        B, views, hw, dim, heads = 2, 24, 16, 1024, 16            # 24 views of 224 x 224: 16 x 16 patches each
+        T = views * hw * hw
+        torch.manual_seed(11)                                     # the same weights on every rank
+        rope = speed3r_b200.RoPE2D(100.0)
+        mod = speed3r_b200.SparseFlashAttentionRope(dim, num_heads=heads, qkv_bias=True, qk_norm=True, rope=rope).to(dev)
+        pos = _grid_positions(B, views, hw, hw).to(dev)
+        def batch(seed):
+            g = torch.Generator(device=dev).manual_seed(seed)
+            return (torch.randn(B, T, dim, device=dev, generator=g) * 0.5, torch.randn(B, T, dim, device=dev, generator=g))
+        # every rank's gradient on its own batch without DDP, averaged over ranks by hand ...
+        grads = []
+        for r in range(world):
+            x, dy = batch(100 + r)
+            mod.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = mod(x, xpos=pos)
+            y.float().backward(dy)
+            grads.append([p.grad.detach().clone() for p in mod.parameters()])
+        mean = [sum(gs) / world for gs in zip(*grads)]
+        # ... against one DDP step in which every rank sees only its own batch
+        mod.zero_grad(set_to_none=True)
+        ddp = DDP(mod, device_ids=[rank])
+        x, dy = batch(100 + rank)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = ddp(x, xpos=pos)
+        y.float().backward(dy)
+        torch.cuda.synchronize()
+        ok = True
+        for (name, p), m in zip(mod.named_parameters(), mean):
+            err = (p.grad - m).abs().max().item()
+            if err > 1e-3 * max(1.0, m.abs().max().item()):
+                print(f"rank {rank}: {name} grad differs by {err}", flush=True)
+                ok = False
+        flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            result.put(bool(flag.item() == 1.0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_data_parallel_training_step():
+    """The reference's training configuration (B=2 per GPU, 24 views of 224 x 224 -> 6144 tokens per sample,
+    DistributedDataParallel): one forward + backward of the module under DDP gives every rank the mean of
+    the per-rank gradients (the kernels are deterministic, so the only difference is the all-reduce's order)."""
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = 29500 + (os.getpid() % 500) + 9
+    procs = [ctx.Process(target=_ddp_worker, args=(r, world, port, result)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(600)
+    assert all(pr.exitcode == 0 for pr in procs), [pr.exitcode for pr in procs]
+    assert result.get(timeout=5) is True
