@@ -391,6 +391,76 @@ def run_model(args):
         dist.destroy_process_group()
 
 
+def run_train_step(args):
+    """One data-parallel training step of the attention module at the reference's training size (BASELINE
+    config 5: B=2 per GPU, 24 views of 224x224 -> 6144 tokens per sample, dim 1024, 16 heads, bf16 autocast,
+    DistributedDataParallel as in trainers/base_trainer_accelerate.py:102): forward, backward with the
+    gradient all-reduce, and an AdamW update of the module's parameters.  Weak scaling (the per-GPU batch is fixed)."""
+    import torch
+    import torch.distributed as dist
+    import speed3r_b200
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, views, hw, dim = 2, 24, 16, H * D
+    T = views * hw * hw
+    torch.manual_seed(0)
+    mod = speed3r_b200.SparseFlashAttentionRope(dim, num_heads=H, qkv_bias=True, proj_bias=True, qk_norm=True,
+                                                rope=speed3r_b200.RoPE2D(100.0)).to(dev)
+    net = torch.nn.parallel.DistributedDataParallel(mod, device_ids=[local_rank]) if world > 1 else mod
+    opt = torch.optim.AdamW(mod.parameters(), lr=1e-4)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn(B, T, dim, device=dev, generator=g) * 0.5
+    dy = torch.randn(B, T, dim, device=dev, generator=g) * 0.1
+    tok = torch.arange(T, device=dev) % (hw * hw)
+    xpos = torch.stack((tok // hw, tok % hw), -1)[None].expand(B, -1, -1).contiguous()
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = net(x, xpos=xpos)
+        y.float().backward(dy)
+        opt.step()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    status = _lib_status()
+    if rank == 0:
+        print(json.dumps(dict(
+            metric="attention_module_train_tokens_per_s", value=world * B * T / (ms * 1e-3), unit="tokens/s", n_gpus=world,
+            steps=args.steps, warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, scaling="weak",
+            vs_baseline=None, dtype="bf16", data="synthetic",
+            config={"workload": "SparseFlashAttentionRope forward + backward + AdamW step, B=2 per GPU, 24 views of 224x224 "
+                                "(T=6144 per sample), dim 1024, 16 heads", "global_batch": world * B, "tokens_per_sample": T,
+                    "parallelism": f"ddp{world}" if world > 1 else "single"},
+            device_status=status)))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _lib_status():
+    from speed3r_b200 import _lib
+    return _lib.device_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,6 +482,9 @@ def main():
     ap.add_argument("--gather", default="nccl", choices=["peer", "nccl"],
                     help="N > 1: token-level K/V exchange by an NCCL all-gather on a side stream (default, measured "
                          "fastest) or by this library's peer pull kernel over CUDA IPC")
+    ap.add_argument("--train-step", action="store_true",
+                    help="time one data-parallel training step of the attention module at the reference's training "
+                         "size (B=2 per GPU, T=6144); prints a line of its own (metric attention_module_train_tokens_per_s)")
     ap.add_argument("--no-triton-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()
@@ -422,6 +495,9 @@ def main():
         return
     if args.model:
         run_model(args)
+        return
+    if args.train_step:
+        run_train_step(args)
         return
 
     import torch
