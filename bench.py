@@ -751,7 +751,7 @@ def main():
         e2e = {"value": (f_cmp + f_sel) / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ems,
                "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)),
                "d2h_bytes_per_step": world * hy.numel() * hy.element_size(),
-               "api": ("speed3r_b200.HostPipeline (K/V by head group, queries by chunk, copies overlapped with kernels)"
+               "api": ("speed3r_b200.HostPipeline (head group by head group: K, V, then queries by chunk; copies overlapped with kernels)"
                        if pipe is not None else "speed3r_b200.seq_parallel.sparse_attention_partitioned on this rank's shard")}
 
     # The whole module (qkv/gate/proj GEMMs + prologue + the op) at the same sequence length, forward, no

@@ -223,6 +223,13 @@ int s3r_sel_attn_bwd(const void* q, const void* k, const void* v, const int32_t*
  * ------------------------------------------------------------------------------------------ */
 int s3r_peer_pull(const void* const* src, void* const* dst, const int64_t* bytes, int nseg, int ctas, void* stream);
 
+/* Strided copy between host and device (rows of `width_bytes` at the two pitches) on `stream`:
+ * cudaMemcpy2DAsync with the direction inferred from the pointers.  No counterpart in the reference;
+ * the pinned-host pipeline uses it to place one head group's columns of y [B,T,H*d] in the caller's
+ * buffer (PyTorch stages such a copy through pageable memory and blocks). */
+int s3r_copy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t rows, void* stream);
+
 /* CUDA IPC for those sources.  s3r_ipc_export: the 64-byte handle of the allocation that holds `ptr` and
  * `ptr`'s offset in it (the owner keeps the buffer alive).  s3r_ipc_import: opens such a handle in another
  * process of the same node WITH THE IMPORTER'S DEVICE CURRENT (lazy peer access), so that kernels of that

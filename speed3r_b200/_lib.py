@@ -32,6 +32,7 @@ SIGNATURES = {
     "s3r_merge_bwd": (_i, [_p, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "s3r_delta": (_i, [_p, _p, _p, _i64, _i, _p]),
     "s3r_sel_attn_bwd": (_i, [_p] * 12 + [_i, _i, _i, _i, _i, _i, _i, _f, _p]),
+    "s3r_copy2d_async": (_i, [_p, _sz, _p, _sz, _sz, _sz, _p]),
     "s3r_peer_pull": (_i, [_p, _p, _p, _i, _i, _p]),
     "s3r_ipc_export": (_i, [_p, _p, C.POINTER(C.c_int64)]),
     "s3r_ipc_import": (_i, [_p, _i64, C.POINTER(_p)]),

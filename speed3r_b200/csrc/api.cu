@@ -117,4 +117,14 @@ int s3r_device_status(uint32_t* status_host, int clear) {
   return 0;
 }
 
+int s3r_copy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t rows, void* stream) {
+  S3R_REQUIRE(dst && src, S3R_ERR_NULL, "s3r_copy2d_async: NULL pointer");
+  S3R_REQUIRE(width_bytes > 0 && rows > 0 && dst_pitch >= width_bytes && src_pitch >= width_bytes, S3R_ERR_SHAPE,
+              "s3r_copy2d_async: need 0 < width <= both pitches and rows > 0");
+  S3R_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                             static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
 }  // extern "C"

@@ -5,15 +5,17 @@ pi3/models/layers/sparse_attention.py:88-143); a host that holds them in its own
 PCIe copies on top of the kernels.  `HostPipeline` hides most of that cost by cutting the op along
 the two axes on which it is independent and running three streams:
 
-* copy-in stream: K and V arrive head group by head group (a head of a `[1,H,T,d]` tensor is one
-  contiguous span) and are pooled as they land; the queries follow in chunks of query blocks;
-* compute stream: per query chunk, pool -> compression attention + top-k -> selection attention
-  with the gated merge; a chunk needs all pooled K/V but only its own queries;
-* copy-out stream: each chunk of `y [1,T,H*d]` (token-major, so a chunk is contiguous) goes back
-  while the next chunk computes.
+* heads are independent, so the op runs head group by head group: a group's K and V arrive (a head of a
+  `[1,H,T,d]` tensor is one contiguous span) and are pooled as they land, then its queries follow in
+  chunks of query blocks.  The first group computes while the second is still on the bus, so the copy-in
+  stream never waits for the kernels and the kernels only wait for data;
+* compute stream: per (head group, query chunk), pool -> compression attention + top-k -> selection
+  attention with the gated merge; a chunk needs the group's pooled K/V but only its own queries;
+* copy-out stream: each chunk of a group's `y [1,T,Hg*d]` goes back while the next chunk computes, as a
+  strided copy into the group's columns of the caller's `y [1,T,H*d]`.
 
 The query chunk is sized so that one compression-attention launch fills whole waves of the GPU
-(`H * ceil(rows/256)` CTAs a multiple of the SM count).  Results are bit-identical to the unchunked
+(`Hg * ceil(rows/256)` CTAs a multiple of the SM count).  Results are bit-identical to the unchunked
 call: every query row sees the same keys in the same order.
 """
 from __future__ import annotations
@@ -24,9 +26,10 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from . import ops
+from . import _lib, ops
 
 _ROWS_PER_CTA = 256          # pooled query rows one compression-attention CTA owns
+_Q_BUFFERS = 4
 
 
 def rows_per_chunk_for(num_heads: int, sm_count: int) -> int:
@@ -54,11 +57,12 @@ class HostPipeline:
     ``pipe = HostPipeline(H, T, device=...)`` then ``pipe(hq, hk, hv, hgate, hy)`` with pinned host
     tensors ``hq/hk/hv [1,H,T,d]``, ``hgate [1,H,T,2]`` and the result buffer ``hy [1,T,H*d]``.
     The call only enqueues work; the calling stream is made to wait for the last copy, so an event
-    recorded on it (or a synchronize) covers the whole op."""
+    recorded on it (or a synchronize) covers the whole op.  ``heads_per_group`` heads travel and compute
+    together (``heads_per_copy`` is the older name of the same argument)."""
 
     def __init__(self, H: int, T: int, d: int = 64, block_size: int = 16, topk: int = 32,
                  device: Optional[torch.device] = None, rows_per_chunk: Optional[int] = None,
-                 heads_per_copy: int = 2):
+                 heads_per_group: Optional[int] = None, heads_per_copy: Optional[int] = None):
         if T % block_size:
             raise RuntimeError(f"T={T} must be a multiple of the block size {block_size}")
         self.H, self.T, self.d, self.block, self.topk = H, T, d, block_size, topk
@@ -66,24 +70,31 @@ class HostPipeline:
         if self.dev.type != "cuda":
             raise RuntimeError("HostPipeline needs a CUDA device")
         self.Nc = T // block_size
+        hg = heads_per_group if heads_per_group is not None else heads_per_copy
+        self.hg = max(1, min(H, hg if hg is not None else 4))
         if rows_per_chunk is None:
             sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
-            rows_per_chunk = rows_per_chunk_for(H, sms)
+            rows_per_chunk = rows_per_chunk_for(self.hg, sms)
         self.rows = max(1, min(self.Nc, rows_per_chunk))
-        self.heads_per_copy = max(1, min(H, heads_per_copy))
         bf = dict(device=self.dev, dtype=torch.bfloat16)
-        self.k = torch.empty(1, H, T, d, **bf)
-        self.v = torch.empty(1, H, T, d, **bf)
-        self.k_c = torch.empty(1, H, self.Nc, d, **bf)
-        self.v_c = torch.empty(1, H, self.Nc, d, **bf)
-        self.gate = torch.empty(1, H, T, 2, **bf)
+        hg = self.hg
+        # two sets of group buffers: group g+1 lands while group g computes
+        self.k = [torch.empty(1, hg, T, d, **bf) for _ in range(2)]
+        self.v = [torch.empty(1, hg, T, d, **bf) for _ in range(2)]
+        self.gate = [torch.empty(1, hg, T, 2, **bf) for _ in range(2)]
         tc = self.rows * block_size
-        self.qbuf = [torch.empty(1, H, tc, d, **bf) for _ in range(2)]
+        # query chunks may run up to four ahead of the kernels: a chunk computes a little longer than it travels, and
+        # the copy-in stream must not wait for a free buffer while the next group's K and V could be on the bus
+        self.qbuf = [torch.empty(1, hg, tc, d, **bf) for _ in range(_Q_BUFFERS)]
         self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
 
     def chunks(self):
-        """[(first pooled row, last pooled row + 1)] of the query chunks."""
+        """[(first pooled row, last pooled row + 1)] of the query chunks (the same for every head group)."""
         return query_chunks(self.Nc, self.rows)
+
+    def groups(self):
+        """[(first head, last head + 1)] of the head groups; the last may be short."""
+        return [(h, min(self.H, h + self.hg)) for h in range(0, self.H, self.hg)]
 
     @torch.no_grad()
     def __call__(self, hq: Tensor, hk: Tensor, hv: Tensor, hgate: Tensor, hy: Tensor) -> None:
@@ -97,44 +108,56 @@ class HostPipeline:
         s_in, s_out = self.s_in, self.s_out
         s_in.wait_stream(main)            # device buffers may still be read by an earlier call
         s_out.wait_stream(main)
+        lib = _lib.load()
+        esz = hy.element_size()
 
-        # K and V, head group by head group; each group is pooled on the compute stream as it lands
-        hp = self.heads_per_copy
-        for src, dst, dst_c in ((hk, self.k, self.k_c), (hv, self.v, self.v_c)):
-            for h0 in range(0, H, hp):
-                h1 = min(H, h0 + hp)
+        grp_free = [None, None]           # compute of the group that last used buffer set i is finished
+        q_free = [None] * _Q_BUFFERS      # compute of the chunk that last used qbuf[i] is finished
+        step = 0
+        for gi, (h0, h1) in enumerate(self.groups()):
+            b, n = gi & 1, h1 - h0
+            k, v, gate = (buf[b][:, :n] for buf in (self.k, self.v, self.gate))
+            with torch.cuda.stream(s_in):
+                if grp_free[b] is not None:
+                    s_in.wait_event(grp_free[b])
+                k.copy_(hk[:, h0:h1], non_blocking=True)
+                k_in = torch.cuda.Event()
+                k_in.record(s_in)
+                v.copy_(hv[:, h0:h1], non_blocking=True)
+                gate.copy_(hgate[:, h0:h1], non_blocking=True)
+                v_in = torch.cuda.Event()
+                v_in.record(s_in)
+            main.wait_event(k_in)
+            k_c = ops.pool_tokens(k, bs, bs)                      # pooled while V is still on the bus
+            main.wait_event(v_in)
+            v_c = ops.pool_tokens(v, bs, bs)
+            done = None
+            for r0, r1 in self.chunks():
+                i = step % _Q_BUFFERS
+                step += 1
+                t0, t1 = r0 * bs, r1 * bs
+                q_dev = self.qbuf[i].view(-1)[:n * (t1 - t0) * d].view(1, n, t1 - t0, d)
                 with torch.cuda.stream(s_in):
-                    dst[:, h0:h1].copy_(src[:, h0:h1], non_blocking=True)
+                    if q_free[i] is not None:
+                        s_in.wait_event(q_free[i])
+                    for h in range(n):                            # per head: contiguous spans on both sides
+                        q_dev[0, h].copy_(hq[0, h0 + h, t0:t1], non_blocking=True)
                     landed = torch.cuda.Event()
                     landed.record(s_in)
                 main.wait_event(landed)
-                dst_c[:, h0:h1].copy_(ops.pool_tokens(dst[:, h0:h1], bs, bs))
-        with torch.cuda.stream(s_in):
-            self.gate.copy_(hgate, non_blocking=True)
-
-        # queries in chunks: copy-in (per head, contiguous spans) | compute | copy-out
-        q_free = [None, None]             # compute of the chunk that last used qbuf[i] is finished
-        for c, (r0, r1) in enumerate(self.chunks()):
-            i = c & 1
-            t0, t1 = r0 * bs, r1 * bs
-            q_dev = self.qbuf[i].view(-1)[:H * (t1 - t0) * d].view(1, H, t1 - t0, d)
-            with torch.cuda.stream(s_in):
-                if q_free[i] is not None:
-                    s_in.wait_event(q_free[i])
-                for h in range(H):
-                    q_dev[0, h].copy_(hq[0, h, t0:t1], non_blocking=True)
-                landed = torch.cuda.Event()
-                landed.record(s_in)
-            main.wait_event(landed)
-            q_c = ops.pool_tokens(q_dev, bs, bs)
-            o_c, idx = ops.flash_attn_topk_func(q_c, self.k_c, self.v_c, self.topk)
-            y = ops.sel_attn_merge(q_dev, self.k, self.v, idx, self.gate[:, :, t0:t1], o_c, bs)
-            done = torch.cuda.Event()
-            done.record(main)
-            q_free[i] = done
-            y.record_stream(s_out)        # the allocator must not hand y out again before it has left
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                hy[:, t0:t1].copy_(y, non_blocking=True)
+                q_c = ops.pool_tokens(q_dev, bs, bs)
+                o_c, idx = ops.flash_attn_topk_func(q_c, k_c, v_c, self.topk)
+                y = ops.sel_attn_merge(q_dev, k, v, idx, gate[:, :, t0:t1], o_c, bs)      # [1, t1-t0, n*d]
+                done = torch.cuda.Event()
+                done.record(main)
+                q_free[i] = done
+                y.record_stream(s_out)    # the allocator must not hand y out again before it has left
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    # this group's columns of the rows t0..t1 of hy [1,T,H*d]
+                    _lib.check(lib.s3r_copy2d_async(hy.data_ptr() + (t0 * H * d + h0 * d) * esz, H * d * esz,
+                                                    y.data_ptr(), n * d * esz, n * d * esz, t1 - t0,
+                                                    s_out.cuda_stream), "s3r_copy2d_async")
+            grp_free[b] = done
         main.wait_stream(s_out)
         main.wait_stream(s_in)
