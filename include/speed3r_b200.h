@@ -111,6 +111,20 @@ int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, voi
                           int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
                           void* stream);
 
+/* The same kernel for settings in which compressed keys are finer than selection blocks (windows of Lc
+ * tokens every Sc tokens, selection blocks of Bs = group*Sc tokens).  No counterpart in the reference,
+ * whose three sizes are equal.  Queries are pooled per selection block by the caller.
+ *   idx [B,H,Nq,topk] = the `topk` selection BLOCKS of each row by the softmax probability mass of the
+ *         block's own compressed keys, i.e. of columns group*n .. group*n+take-1 (take = (Bs-Lc)/Sc + 1
+ *         windows lie inside a block), ranked through log2 sum_j 2^(scale*log2(e)*s_j) - monotone in the
+ *         mass, no row normaliser needed - with the same order rules (score descending, block
+ *         ascending) and the same padding (Nb-1 when fewer than topk blocks exist).  Only blocks with
+ *         all `take` columns present are ranked: Nb = (Nc-take)/group + 1.
+ *   group must be 4; 1 <= take <= 4.  o_c and lse as above. */
+int s3r_cmp_attn_blocktopk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
+                               int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
+                               int group, int take, void* stream);
+
 /* Backward of the compression attention.  Replaces FlashAttnTopkFunc.backward /
  * _flash_attn_backward and its three kernels (flash_attention_topk.py:204-630).  No gradient
  * flows through idx (:665).

@@ -135,14 +135,34 @@ def topk_rows(scores: torch.Tensor, k: int) -> torch.Tensor:
 # --------------------------------------------------------------------------------------
 # compression attention + top-k  (flash_attention_topk.py:22-152)
 # --------------------------------------------------------------------------------------
+def block_rank_scores(S: torch.Tensor, softmax_scale: float, group: int, take: int) -> torch.Tensor:
+    """Selection score of key block n for every query row when the compressed keys do not map one to one
+    onto selection blocks (no counterpart in the reference, whose three block sizes are equal): the softmax
+    probability mass of the compressed entries whose window lies inside the block.  With windows of ``Lc``
+    tokens every ``Sc`` tokens and blocks of ``Bs`` tokens those are the columns ``group*n ... group*n +
+    take - 1`` with ``group = Bs/Sc`` and ``take = (Bs-Lc)/Sc + 1``.  Ranking by mass is ranking by
+    ``log2 sum_j 2^(c*s_j)`` (``c = softmax_scale*log2 e``), which is what is returned: it needs no row
+    normaliser, so it can be formed while the row is still streaming.  Only blocks with all ``take`` columns
+    present are ranked.  ``S [..., Nq, Nc]`` raw logits -> ``[..., Nq, Nb]`` fp32."""
+    Nc = S.shape[-1]
+    Nb = (Nc - take) // group + 1 if Nc >= take else 0
+    c = softmax_scale * 1.4426950408889634
+    cols = (torch.arange(Nb)[:, None] * group + torch.arange(take)[None, :]).reshape(-1)
+    g = (S.float()[..., cols] * c).reshape(*S.shape[:-1], Nb, take)
+    m = g.max(dim=-1).values
+    return m + torch.log2(torch.exp2(g - m[..., None]).sum(dim=-1))
+
+
 def cmp_attn_topk(q_c, k_c, v_c, topk: int, softmax_scale: Optional[float] = None,
-                  round_p_to: Optional[torch.dtype] = None, row_chunk: int = 4096):
+                  round_p_to: Optional[torch.dtype] = None, row_chunk: int = 4096,
+                  rank_group: Optional[tuple] = None):
     """Dense non-causal attention of pooled queries over pooled keys plus the top-``topk``
     columns of the raw (unscaled) logits of every row.
 
     q_c ``[B,H,Nq,d]``, k_c/v_c ``[B,H,Nc,d]`` -> (o ``[B,H,Nq,d]``, lse ``[B,H,Nq]`` fp32,
     idx ``[B,H,Nq,topk]`` int32).  ``round_p_to`` mimics the kernel's cast of P to the V
-    dtype before the PV product (flash_attention_topk.py:107).
+    dtype before the PV product (flash_attention_topk.py:107).  ``rank_group = (group, take)``
+    ranks selection blocks by ``block_rank_scores`` instead of columns by their logits.
     """
     B, H, Nq, d = q_c.shape
     if softmax_scale is None:
@@ -151,7 +171,7 @@ def cmp_attn_topk(q_c, k_c, v_c, topk: int, softmax_scale: Optional[float] = Non
     for r0 in range(0, Nq, row_chunk):
         q = q_c[:, :, r0:r0 + row_chunk]
         S = torch.matmul(q.float(), k_c.float().transpose(-1, -2))          # raw logits, fp32
-        idxs.append(topk_rows(S, topk))
+        idxs.append(topk_rows(S if rank_group is None else block_rank_scores(S, softmax_scale, *rank_group), topk))
         Ss = S * softmax_scale
         lse = torch.logsumexp(Ss, dim=-1)
         P = torch.exp(Ss - lse[..., None])
@@ -260,9 +280,16 @@ def sparse_attention_op(q, k, v, gate, block: int = 16, topk: int = 32,
                         kernel: int = 16, stride: int = 16):
     """Op-level path used by the op sweeps: pool q,k,v directly (no LN/RoPE), compression
     attention + top-k, selection attention, gated merge.  Inputs ``[B,H,T,d]``, gate
-    ``[B,H,T,2]`` (already passed through the sigmoid).  Returns (y ``[B,T,H*d]``, idx)."""
+    ``[B,H,T,2]`` (already passed through the sigmoid).  Returns (y ``[B,T,H*d]``, idx).
+    Queries are pooled per selection block; keys and values with ``kernel``/``stride``.  At the reference's
+    16/16/16 this is its path; for other settings the blocks are ranked by ``block_rank_scores``."""
     q_c, k_c, v_c = pool_tokens(q, block, block), pool_tokens(k, kernel, stride), pool_tokens(v, kernel, stride)
-    o_c, _, idx = cmp_attn_topk(q_c, k_c, v_c, topk)
+    rank_group = None
+    if (kernel, stride) != (block, block):        # compressed keys and selection blocks differ: rank blocks by mass
+        if block % stride or kernel > block or (block - kernel) % stride:
+            raise ValueError("need stride | block and kernel = block - i*stride")
+        rank_group = (block // stride, (block - kernel) // stride + 1)
+    o_c, _, idx = cmp_attn_topk(q_c, k_c, v_c, topk, rank_group=rank_group)
     o_s, _ = sel_attn(q, k, v, idx, block)
     return gated_merge(gate, o_c, o_s, block), idx
 

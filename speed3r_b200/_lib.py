@@ -23,6 +23,7 @@ SIGNATURES = {
     "s3r_pool_bwd": (_i, [_p, _p, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p]),
     "s3r_qkv_prologue_fwd": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "s3r_cmp_attn_topk_fwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
+    "s3r_cmp_attn_blocktopk_fwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p]),
     "s3r_cmp_attn_bwd": (_i, [_p] * 10 + [_i, _i, _i, _i, _i, _f, _p]),
     "s3r_sel_attn_fwd": (_i, [_p, _p, _p, _i, _i64, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p,
                               _i, _i, _i, _i, _i, _i, _i, _f, _p]),

@@ -80,6 +80,7 @@ struct CmpParams {
   float* lse;
   int32_t* idx;
   int Nq, Nc, topk;
+  int n_rank, rank_take;   // block ranking (RANK = 1): number of ranked blocks, columns counted per group of 4
   float c_scale;        // softmax scale * log2(e)
   uint32_t* status;
 };
@@ -164,6 +165,11 @@ __device__ __noinline__ void topk_merge_own(uint2* my_list, const uint2* my_pend
   cnt = 0;
 }
 
+// RANK = 0: the table holds the top-k COLUMNS of each row by raw logit (the reference's setting, where a
+// compressed key is a selection block).  RANK = 1: compressed keys are finer than selection blocks (windows of
+// Lc tokens every Sc, blocks of Bs = 4*Sc); the table holds the top-k BLOCKS by the softmax mass of the
+// block's own columns 4n .. 4n+take-1, ranked through log2 sum_j 2^(c*s_j), which needs no row normaliser.
+template <int RANK>
 __global__ void __launch_bounds__(kCmpThreads, 1)
 cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const CmpParams p) {
@@ -558,6 +564,37 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
       };
 
+      // Block ranking: the 16 columns of a chunk are four groups of four; a group's score is
+      // log2 sum 2^(c*s) over its first `rank_take` columns.  Hits are appended in ascending block order.
+      auto handle_blocks = [&](uint32_t (&x)[16], int c8) {
+        const int gbase = (col0 + c8 * 16) >> 2;
+        const float cs = p.c_scale;
+        float r[4];
+        bool valid[4];
+#pragma unroll
+        for (int gi = 0; gi < 4; ++gi) {
+          float a[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) a[e] = (e < p.rank_take) ? __uint_as_float(x[4 * gi + e]) * cs : -INFINITY;
+          const float m = fmaxf(fmax3(a[0], a[1], a[2]), a[3]);
+          const float sum = (fast_exp2(a[0] - m) + fast_exp2(a[1] - m)) + (fast_exp2(a[2] - m) + fast_exp2(a[3] - m));
+          valid[gi] = gbase + gi < p.n_rank;            // all of the group's counted columns exist
+          r[gi] = valid[gi] ? m + fast_log2(sum) : -INFINITY;
+        }
+        const float cm = fmaxf(fmaxf(r[0], r[1]), fmaxf(r[2], r[3]));
+        if (!__any_sync(0xffffffffu, cm > thr || (thr == -INFINITY && (valid[0] || valid[1] || valid[2] || valid[3])))) return;
+#pragma unroll
+        for (int gi = 0; gi < 4; ++gi) {
+          // an empty slot (thr = -inf) takes any ranked block, whatever its score
+          const bool hit = valid[gi] && (r[gi] > thr || thr == -INFINITY);
+          while (__any_sync(0xffffffffu, hit && cnt >= kPend)) topk_merge_own(my_list, my_pend, cnt, thr, topk);
+          if (hit) {
+            my_pend[cnt * 32] = make_uint2(sortable_key(r[gi]), static_cast<uint32_t>(gbase + gi));
+            ++cnt;
+          }
+        }
+      };
+
       // tensor-memory loads run one chunk ahead of the handling
       uint32_t xa[16], xb[16];
       tmem_ld16(t_s, xa);
@@ -565,7 +602,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int c8 = 0; c8 < 8; c8 += 2) {
         tmem_ld_wait();
         tmem_ld16(t_s + (c8 + 1) * 16, xb);
-        handle(xa, c8);
+        if (RANK == 0) handle(xa, c8); else handle_blocks(xa, c8);
         tmem_ld_wait();
         if (c8 + 2 < 8) {
           tmem_ld16(t_s + (c8 + 2) * 16, xa);
@@ -573,7 +610,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tc_fence_before();
           mbar_arrive(&ctl.tk_done[t]);
         }
-        handle(xb, c8 + 1);
+        if (RANK == 0) handle(xb, c8 + 1); else handle_blocks(xb, c8 + 1);
       }
       // the tile is already released; merge the pending hits every few tiles, or early when some
       // buffer is nearly full
@@ -592,7 +629,7 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint2 ent = warp_lists[lane * 32 + r];
         if (lane < topk)
           p.idx[(static_cast<int64_t>(bh) * p.Nq + wrow0 + r) * topk + lane] =
-              (ent.x == 0u) ? (p.Nc - 1) : static_cast<int32_t>(~ent.y);
+              (ent.x == 0u) ? ((RANK == 0 ? p.Nc : p.n_rank) - 1) : static_cast<int32_t>(~ent.y);
       }
     }
     if (!ok && lane == 0) atomicOr(p.status, kStatusWaitTimeout);
@@ -607,18 +644,18 @@ cmp_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 using namespace s3r;
 
-extern "C" int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
-                                     int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
-                                     void* stream) {
-  S3R_REQUIRE(q_c && k_c && v_c && o_c && lse && idx, S3R_ERR_NULL, "s3r_cmp_attn_topk_fwd: NULL pointer");
-  S3R_REQUIRE(B > 0 && H > 0 && Nq > 0 && Nc > 0, S3R_ERR_SHAPE,
-              "s3r_cmp_attn_topk_fwd: sizes must be positive (B=%d H=%d Nq=%d Nc=%d)", B, H, Nq, Nc);
-  S3R_REQUIRE(d == 64, S3R_ERR_UNSUPPORTED, "s3r_cmp_attn_topk_fwd: head_dim %d not supported (64 only)", d);
-  S3R_REQUIRE(topk >= 1 && topk <= 32, S3R_ERR_UNSUPPORTED, "s3r_cmp_attn_topk_fwd: topk %d not in [1,32]", topk);
-  S3R_REQUIRE(scale > 0.f, S3R_ERR_UNSUPPORTED, "s3r_cmp_attn_topk_fwd: softmax scale must be positive");
+static int launch_cmp_fwd(const char* who, const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
+                          int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale, int rank_take,
+                          void* stream) {
+  S3R_REQUIRE(q_c && k_c && v_c && o_c && lse && idx, S3R_ERR_NULL, "%s: NULL pointer", who);
+  S3R_REQUIRE(B > 0 && H > 0 && Nq > 0 && Nc > 0, S3R_ERR_SHAPE, "%s: sizes must be positive (B=%d H=%d Nq=%d Nc=%d)", who,
+              B, H, Nq, Nc);
+  S3R_REQUIRE(d == 64, S3R_ERR_UNSUPPORTED, "%s: head_dim %d not supported (64 only)", who, d);
+  S3R_REQUIRE(topk >= 1 && topk <= 32, S3R_ERR_UNSUPPORTED, "%s: topk %d not in [1,32]", who, topk);
+  S3R_REQUIRE(scale > 0.f, S3R_ERR_UNSUPPORTED, "%s: softmax scale must be positive", who);
   const uintptr_t al = reinterpret_cast<uintptr_t>(q_c) | reinterpret_cast<uintptr_t>(k_c) |
                        reinterpret_cast<uintptr_t>(v_c) | reinterpret_cast<uintptr_t>(o_c);
-  S3R_REQUIRE((al & 15) == 0, S3R_ERR_ALIGNMENT, "s3r_cmp_attn_topk_fwd: tensors must be 16-byte aligned");
+  S3R_REQUIRE((al & 15) == 0, S3R_ERR_ALIGNMENT, "%s: tensors must be 16-byte aligned", who);
   const int BH = B * H;
   CUtensorMap mq, mk, mv;
   uint32_t box[3] = {64, 128, 1};
@@ -641,15 +678,38 @@ extern "C" int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const voi
   p.lse = lse;
   p.idx = idx;
   p.Nq = Nq; p.Nc = Nc; p.topk = topk;
+  p.rank_take = rank_take;
+  p.n_rank = rank_take > 0 ? (Nc - rank_take) / 4 + 1 : 0;      // groups of four columns with all counted columns present
   p.c_scale = scale * 1.4426950408889634f;
   p.status = device_status_ptr();
-  S3R_REQUIRE(p.status != nullptr, S3R_ERR_DRIVER, "s3r_cmp_attn_topk_fwd: could not resolve the device status word");
+  S3R_REQUIRE(p.status != nullptr, S3R_ERR_DRIVER, "%s: could not resolve the device status word", who);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // per device and idempotent: setting it on every call keeps this entry point free of process-global state
-  S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmpSmemBytes));
   const int64_t grid = static_cast<int64_t>(BH) * ((Nq + 255) / 256);
-  S3R_REQUIRE(grid < (1ll << 31), S3R_ERR_TOO_LARGE, "s3r_cmp_attn_topk_fwd: grid too large");
-  cmp_fwd_kernel<<<static_cast<unsigned>(grid), kCmpThreads, kCmpSmemBytes, st>>>(mq, mk, mv, p);
+  S3R_REQUIRE(grid < (1ll << 31), S3R_ERR_TOO_LARGE, "%s: grid too large", who);
+  // per device and idempotent: setting it on every call keeps the entry points free of process-global state
+  if (rank_take == 0) {
+    S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmpSmemBytes));
+    cmp_fwd_kernel<0><<<static_cast<unsigned>(grid), kCmpThreads, kCmpSmemBytes, st>>>(mq, mk, mv, p);
+  } else {
+    S3R_CUDA(cudaFuncSetAttribute(cmp_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCmpSmemBytes));
+    cmp_fwd_kernel<1><<<static_cast<unsigned>(grid), kCmpThreads, kCmpSmemBytes, st>>>(mq, mk, mv, p);
+  }
   S3R_CUDA(cudaGetLastError());
   return 0;
+}
+
+extern "C" int s3r_cmp_attn_topk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
+                                     int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
+                                     void* stream) {
+  return launch_cmp_fwd("s3r_cmp_attn_topk_fwd", q_c, k_c, v_c, o_c, lse, idx, B, H, Nq, Nc, d, topk, scale, 0, stream);
+}
+
+extern "C" int s3r_cmp_attn_blocktopk_fwd(const void* q_c, const void* k_c, const void* v_c, void* o_c, float* lse,
+                                          int32_t* idx, int B, int H, int Nq, int Nc, int d, int topk, float scale,
+                                          int group, int take, void* stream) {
+  S3R_REQUIRE(group == 4, S3R_ERR_UNSUPPORTED, "s3r_cmp_attn_blocktopk_fwd: %d compressed keys per block (4 only)", group);
+  S3R_REQUIRE(take >= 1 && take <= 4 && Nc >= take, S3R_ERR_UNSUPPORTED,
+              "s3r_cmp_attn_blocktopk_fwd: take=%d must be in [1,4] and <= Nc=%d", take, Nc);
+  return launch_cmp_fwd("s3r_cmp_attn_blocktopk_fwd", q_c, k_c, v_c, o_c, lse, idx, B, H, Nq, Nc, d, topk, scale, take,
+                        stream);
 }

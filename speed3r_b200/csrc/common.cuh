@@ -67,6 +67,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float fast_log2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // max of three in one instruction (three-operand max of sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;

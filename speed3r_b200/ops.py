@@ -161,6 +161,32 @@ def _(q_c, k_c, v_c, topk, scale):
             q_c.new_empty(B, H, Nq, topk, dtype=torch.int32))
 
 
+@torch.library.custom_op("speed3r_b200::cmp_attn_blocktopk_fwd", mutates_args=())
+def _cmp_block_fwd(q_c: Tensor, k_c: Tensor, v_c: Tensor, topk: int, scale: float, group: int,
+                   take: int) -> Tuple[Tensor, Tensor, Tensor]:
+    for n, t in (("q_c", q_c), ("k_c", k_c), ("v_c", v_c)):
+        _need(t, n)
+    B, H, Nq, d = q_c.shape
+    Nc = k_c.shape[2]
+    if k_c.shape != (B, H, Nc, d) or v_c.shape != (B, H, Nc, d):
+        raise RuntimeError(f"k_c/v_c shape mismatch: {tuple(k_c.shape)} {tuple(v_c.shape)} vs B={B} H={H} d={d}")
+    o = torch.empty_like(q_c)
+    lse = torch.empty(B, H, Nq, device=q_c.device, dtype=torch.float32)
+    idx = torch.empty(B, H, Nq, topk, device=q_c.device, dtype=torch.int32)
+    with torch.cuda.device(q_c.device):
+        _lib.check(_lib.load().s3r_cmp_attn_blocktopk_fwd(q_c.data_ptr(), k_c.data_ptr(), v_c.data_ptr(), o.data_ptr(),
+                                                          lse.data_ptr(), idx.data_ptr(), B, H, Nq, Nc, d, topk, scale,
+                                                          group, take, _stream()), "s3r_cmp_attn_blocktopk_fwd")
+    return o, lse, idx
+
+
+@_cmp_block_fwd.register_fake
+def _(q_c, k_c, v_c, topk, scale, group, take):
+    B, H, Nq, d = q_c.shape
+    return (torch.empty_like(q_c), q_c.new_empty(B, H, Nq, dtype=torch.float32),
+            q_c.new_empty(B, H, Nq, topk, dtype=torch.int32))
+
+
 @torch.library.custom_op("speed3r_b200::cmp_attn_bwd", mutates_args=())
 def _cmp_bwd(q_c: Tensor, k_c: Tensor, v_c: Tensor, o_c: Tensor, lse: Tensor, do_c: Tensor,
              scale: float) -> Tuple[Tensor, Tensor, Tensor]:
@@ -361,6 +387,51 @@ class _FlashAttnTopk(torch.autograd.Function):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = _cmp_bwd(q, k, v, o, lse, do.contiguous(), ctx.scale)
         return dq, dk, dv, None, None
+
+
+class _FlashAttnBlockTopk(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, topk, scale, group, take):
+        q, k, v = [x if x.is_contiguous() else x.contiguous() for x in (q, k, v)]
+        o, lse, idx = _cmp_block_fwd(q, k, v, topk, scale, group, take)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale = scale
+        ctx.mark_non_differentiable(idx)
+        return o, idx
+
+    @staticmethod
+    def backward(ctx, do, _didx):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = _cmp_bwd(q, k, v, o, lse, do.contiguous(), ctx.scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attn_blocktopk_func(q, k, v, topk_val, group, take, softmax_scale=None):
+    """Compression attention whose table ranks selection BLOCKS by the softmax mass of their own compressed
+    keys (columns ``group*n .. group*n+take-1``): for settings where compressed keys are finer than selection
+    blocks.  Returns ``(o, idx)`` like ``flash_attn_topk_func``; ``idx`` holds block numbers."""
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    return _FlashAttnBlockTopk.apply(q, k, v, int(topk_val), float(softmax_scale), int(group), int(take))
+
+
+def sparse_attention_op(q, k, v, gate, block_size=16, topk=32, kernel=16, stride=16):
+    """The whole op on ``q,k,v [B,H,T,d]`` and ``gate [B,H,T,2]``: queries pooled per selection block
+    (``block_size`` tokens), keys and values pooled with ``kernel``/``stride``, compression attention with the
+    fused table, selection attention over the table's blocks, gated merge.  At 16/16/16 this is the
+    reference's path (``sparse_attention.py:95-136`` without the norms and rotary embedding); when compressed
+    keys are finer than selection blocks (e.g. kernel 32, stride 16, blocks of 64) the blocks are ranked by
+    probability mass.  Returns ``(y [B,T,H*d], idx)``."""
+    q_c = pool_tokens(q, block_size, block_size)
+    k_c, v_c = pool_tokens(k, kernel, stride), pool_tokens(v, kernel, stride)
+    if (kernel, stride) == (block_size, block_size):
+        o_c, idx = flash_attn_topk_func(q_c, k_c, v_c, topk)
+    else:
+        if block_size % stride or kernel > block_size or (block_size - kernel) % stride:
+            raise RuntimeError("need stride | block_size and kernel = block_size - i*stride")
+        o_c, idx = flash_attn_blocktopk_func(q_c, k_c, v_c, topk, block_size // stride,
+                                             (block_size - kernel) // stride + 1)
+    return sel_attn_merge(q, k, v, idx, gate, o_c, block_size), idx
 
 
 def flash_attn_topk_func(q, k, v, topk_val, bias=None, causal=False, softmax_scale=None):

@@ -198,6 +198,51 @@ def test_sel_attn_backward_sink_blocks():
     assert float(kg.grad[:, :, (nb // 2 + 1) * Bs:(nb - 1) * Bs].abs().max()) == 0.0   # unselected blocks: exact zeros
 
 
+@pytest.mark.parametrize("B,H,T,Lc,Sc,Bs,K", [(1, 2, 4096, 32, 16, 64, 16), (2, 2, 2112, 32, 16, 64, 16),
+                                              (1, 2, 3072, 16, 16, 64, 8), (1, 1, 1024, 64, 16, 64, 32)])
+def test_extension_setting_block_ranking(B, H, T, Lc, Sc, Bs, K):
+    """Compressed keys finer than selection blocks (windows of Lc every Sc tokens, blocks of Bs = 4*Sc): the
+    table ranks blocks by the softmax mass of their own compressed keys.  The oracle is the definition
+    (`block_rank_scores`); entries may differ only where the competing block scores are closer than 1e-3."""
+    from speed3r_b200 import ops
+    q, k, v = bf16_round(randn(51, B, H, T, 64), randn(52, B, H, T, 64), randn(53, B, H, T, 64))
+    gate, = bf16_round(torch.sigmoid(randn(54, B, H, T, 2)))
+    group, take = Bs // Sc, (Bs - Lc) // Sc + 1
+    q_c, k_c, v_c = R.pool_tokens(q, Bs, Bs), R.pool_tokens(k, Lc, Sc), R.pool_tokens(v, Lc, Sc)
+    q_c, k_c, v_c = bf16_round(q_c, k_c, v_c)
+    o_ref, lse_ref, idx_ref = R.cmp_attn_topk(q_c, k_c, v_c, K, rank_group=(group, take))
+    o, idx = ops.flash_attn_blocktopk_func(dev(q_c), dev(k_c), dev(v_c), K, group, take)
+    assert_bf16_close(o, o_ref, "o_c")
+    idx = idx.cpu()
+    Nb = (k_c.shape[2] - take) // group + 1
+    assert int(idx.max()) < Nb and int(idx.min()) >= 0
+    scores = R.block_rank_scores(torch.matmul(q_c.float(), k_c.float().transpose(-1, -2)), 0.125, group, take)
+    kk = min(K, Nb)
+    mism = idx[..., :kk] != idx_ref[..., :kk]
+    if mism.any():                                   # only near-ties may differ
+        a = torch.gather(scores, -1, idx[..., :kk].long())
+        b = torch.gather(scores, -1, idx_ref[..., :kk].long())
+        assert float((a - b).abs()[mism].max()) < 1e-3, "block table differs beyond near-ties"
+        assert mism.float().mean() < 0.02
+    if Nb < K:
+        assert torch.all(idx[..., Nb:] == Nb - 1)    # padding, as the column table pads with Nc-1
+    # the whole op at this setting, forward and backward, given the table the GPU selected
+    qg, kg, vg = (dev(t).requires_grad_(True) for t in (q, k, v))
+    y, idx_op = ops.sparse_attention_op(qg, kg, vg, dev(gate), Bs, K, Lc, Sc)
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    qc_r, kc_r, vc_r = R.pool_tokens(qr, Bs, Bs), R.pool_tokens(kr, Lc, Sc), R.pool_tokens(vr, Lc, Sc)
+    oc_r, _, _ = R.cmp_attn_topk(qc_r, kc_r, vc_r, K, rank_group=(group, take))
+    os_r, _ = R.sel_attn(qr, kr, vr, idx_op.cpu(), Bs)
+    y_ref = R.gated_merge(gate, oc_r, os_r, Bs)
+    assert_bf16_close(y, y_ref, "y")
+    dy, = bf16_round(randn(55, B, T, H * 64))
+    y_ref.backward(dy)
+    y.backward(dev(dy))
+    assert_bf16_close(qg.grad, qr.grad, "dq")
+    assert_bf16_close(kg.grad, kr.grad, "dk")
+    assert_bf16_close(vg.grad, vr.grad, "dv")
+
+
 def test_sel_attn_merge_fused_fwd_bwd():
     from speed3r_b200 import ops
     B, H, T, Bs, K = 2, 4, 656, 16, 32

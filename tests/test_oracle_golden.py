@@ -150,3 +150,24 @@ def test_prologue_restatement_is_the_module_prologue():
                          (sd["k_norm.weight"], sd["k_norm.bias"]))
     for name, t in zip(("q", "k", "v", "q_c", "k_c", "v_c"), out):
         assert torch.equal(t, aux[name]), name
+
+
+def test_block_ranking_reduces_to_column_ranking():
+    """The block-mass ranking of settings with finer compressed keys (no counterpart in the reference) is the
+    reference's column ranking when every block has exactly one compressed key, and at kernel 32 / stride 16 /
+    blocks of 64 it ranks a block by its three inner windows only."""
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(1, 2, 1024, 64, generator=g) for _ in range(3))
+    gate = torch.sigmoid(torch.randn(1, 2, 1024, 2, generator=g))
+    qc, kc, vc = (R.pool_tokens(t, 16, 16) for t in (q, k, v))
+    _, _, idx_cols = R.cmp_attn_topk(qc, kc, vc, 8)
+    _, _, idx_blocks = R.cmp_attn_topk(qc, kc, vc, 8, rank_group=(1, 1))
+    assert torch.equal(idx_cols, idx_blocks)
+    y, idx = R.sparse_attention_op(q, k, v, gate, block=64, topk=4, kernel=32, stride=16)
+    assert y.shape == (1, 1024, 128) and idx.shape == (1, 2, 16, 4) and int(idx.max()) <= 15
+    S = torch.matmul(R.pool_tokens(q, 64, 64), R.pool_tokens(k, 32, 16).transpose(-1, -2))
+    r = R.block_rank_scores(S, 0.125, 4, 3)
+    P = torch.softmax(S * 0.125, -1)
+    mass = torch.stack([P[..., 4 * n:4 * n + 3].sum(-1) for n in range(16)], -1)
+    assert torch.equal(r.argsort(-1, descending=True)[..., :4], mass.argsort(-1, descending=True)[..., :4])
+    assert torch.equal(idx.long(), torch.argsort(r, dim=-1, descending=True, stable=True)[..., :4])
