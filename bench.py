@@ -456,6 +456,61 @@ def run_train_step(args):
         dist.destroy_process_group()
 
 
+def run_extension(args):
+    """The op at BASELINE's other setting - keys/values pooled with kernel 32 and stride 16, selection blocks of
+    64 tokens, top-16 - forward on one GPU, same inputs as the default workload.  Queries are pooled per
+    selection block and the table ranks blocks by the softmax mass of their three inner compressed keys (the
+    reference has no such mode: its three sizes are equal; the oracle's `block_rank_scores` is the definition)."""
+    import torch
+    from speed3r_b200 import ops, _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Lc, Sc, Bs, K = 32, 16, 64, 16
+    T = args.views * TOK_PER_VIEW
+    T -= T % Bs
+    q, k, v, gate = make_inputs(args, T, dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    marks = []
+
+    def step():
+        e = [ev() for _ in range(4)]
+        e[0].record()
+        q_c, k_c, v_c = ops.pool_tokens(q, Bs, Bs), ops.pool_tokens(k, Lc, Sc), ops.pool_tokens(v, Lc, Sc)
+        e[1].record()
+        o_c, idx = ops.flash_attn_blocktopk_func(q_c, k_c, v_c, K, Bs // Sc, (Bs - Lc) // Sc + 1)
+        e[2].record()
+        y = ops.sel_attn_merge(q, k, v, idx, gate, o_c, Bs)
+        e[3].record()
+        marks.append(e)
+        return y
+
+    with torch.no_grad():
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        marks.clear()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(args.steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    avg = lambda i: sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)
+    Nq, Nc = T // Bs, (T - Lc) // Sc + 1
+    f_cmp, f_sel = 4.0 * Nq * Nc * D * H, 4.0 * T * K * Bs * D * H
+    print(json.dumps(dict(
+        metric="sparse_attn_layer_effective_tflops", value=(f_cmp + f_sel) / (ms * 1e-3) / 1e12, unit="TFLOP/s", n_gpus=1,
+        steps=args.steps, warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, scaling="strong",
+        vs_baseline=None, dtype="bf16", data="synthetic",
+        config={"workload": f"sparse global-attention op, fwd, {args.views} views x {TOK_PER_VIEW} tokens (T={T}), H={H}, d={D}, "
+                            f"pool {Lc}/{Sc}, select block {Bs}, top-{K}, blocks ranked by probability mass, {args.inputs} inputs",
+                "tokens": T, "views": args.views, "parallelism": "single"},
+        kernels={"pool_ms": avg(0), "cmp_attn_blocktopk_ms": avg(1), "sel_attn_merge_ms": avg(2),
+                 "cmp_tflops": f_cmp / avg(1) / 1e9, "sel_tflops": f_sel / avg(2) / 1e9},
+        device_status=_lib.device_status())))
+
+
 def _lib_status():
     from speed3r_b200 import _lib
     return _lib.device_status()
@@ -485,6 +540,9 @@ def main():
     ap.add_argument("--train-step", action="store_true",
                     help="time one data-parallel training step of the attention module at the reference's training "
                          "size (B=2 per GPU, T=6144); prints a line of its own (metric attention_module_train_tokens_per_s)")
+    ap.add_argument("--setting", default="reference", choices=["reference", "extension"],
+                    help="reference: pool 16/16, blocks of 16, top-32 (the reference's only setting); extension: pool 32/16, "
+                         "blocks of 64, top-16 with block ranking by probability mass (1 GPU, forward; a line of its own)")
     ap.add_argument("--no-triton-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()
@@ -498,6 +556,9 @@ def main():
         return
     if args.train_step:
         run_train_step(args)
+        return
+    if args.setting == "extension":
+        run_extension(args)
         return
 
     import torch
