@@ -14,8 +14,8 @@
 // One template covers both: the CTA's own tiles X0, X1 (K,V or Q,dO) are the A operands of the first
 // products, the streamed tiles Y0, Y1 (64 rows; Q,dO or K,V) their B operands (K-major) and, read with
 // the other descriptor, the B operands of the second products (N contiguous).
-// What bounds the kernels is the streamed operand traffic from L2 (every CTA reads the whole streamed
-// tensors): bytes per score = 256 / owned rows, so a CTA owns 256 rows - as many as tensor memory holds
+// Every CTA reads the whole streamed tensors from L2: bytes per score = 256 / owned rows (254 GB for both
+// kernels at 1000 views with 128 owned rows), so a CTA owns 256 rows - as many as tensor memory holds
 // accumulators for (2 row tiles x (dK, dV) x 64 columns = 256 columns; the other 256 hold S and dP).
 // Roles: warp 0 TMA producer, warp 1 tcgen05.mma issuer, warp 2 tensor-memory allocator, warp 3 loads the
 // streamed rows' lse/delta (dK/dV kernel), warps 4-7 and 8-11 one compute warpgroup per row tile.  P and dS

@@ -4,9 +4,10 @@
 //   dQ    : one warp per 16 query rows, looping over the key blocks its query block selected
 //   dK/dV : one warp per 16 key rows, looping over the query blocks that selected its key block
 //           (CSR lists, ascending query block => a fixed summation order, no atomics on floats)
-// Both stream 16-row tiles through a two-stage cp.async ring private to the warp and use the
-// mma.sync building blocks of bwd_common.cuh.  They are bounded by gather bandwidth like the
-// forward (16..64 flop per byte).
+// Both stream 16-row tiles through a cp.async ring private to the warp (two stages for dQ, whose list
+// sits in shared memory; three for dK/dV, which also fetches its list and the rows' statistics ahead) and
+// use the mma.sync building blocks of bwd_common.cuh.  Both gather ~130 GB of 128-byte rows out of L2 at
+// 1000 views (16..64 flop per byte): dQ 16 ms, dK/dV 22 ms.
 #include <mutex>
 
 #include "bwd_common.cuh"
