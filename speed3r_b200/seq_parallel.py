@@ -154,6 +154,14 @@ def chunks_to_dense(xc: Tensor) -> Tensor:
     return xc.permute(1, 2, 0, 3, 4).reshape(B, H, G * n, d)
 
 
+def all_gather_pooled(k_c: Tensor, v_c: Tensor, group=None) -> Tuple[Tensor, Tensor]:
+    """Pooled keys and values of all ranks as dense ``[B,H,Nc,d]`` tensors, through ONE all-gather (the
+    compression kernel waits for both, and at eight ranks a second collective launch is a visible share of
+    the step)."""
+    g = all_gather_chunks(torch.stack((k_c, v_c)), group)            # [G,2,B,H,n,d]
+    return chunks_to_dense(g[:, 0]), chunks_to_dense(g[:, 1])
+
+
 def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, block: int, topk: int,
                                  pool: Callable, cmp_attn_topk: Callable, sel_attn_merge: Callable,
                                  group=None, side_stream: Optional["torch.cuda.Stream"] = None, side_group=None,
@@ -184,8 +192,7 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
         pk.stage(k)
         pv.stage(v)
         q_c, k_c, v_c = pooled_local()
-        kc_all = chunks_to_dense(all_gather_chunks(k_c, group))
-        vc_all = chunks_to_dense(all_gather_chunks(v_c, group))
+        kc_all, vc_all = all_gather_pooled(k_c, v_c, group)
         pk.pull()                                              # few CTAs, resident before the attention kernel
         pv.pull()
         o_c, idx = cmp_attn_topk(q_c, kc_all, vc_all, topk)
@@ -199,8 +206,7 @@ def sparse_attention_partitioned(q: Tensor, k: Tensor, v: Tensor, gate: Tensor, 
         with torch.cuda.stream(side_stream):
             k_all, v_all = all_gather_chunks(k, side_group), all_gather_chunks(v, side_group)
     q_c, k_c, v_c = pooled_local()
-    kc_all = chunks_to_dense(all_gather_chunks(k_c, group))
-    vc_all = chunks_to_dense(all_gather_chunks(v_c, group))
+    kc_all, vc_all = all_gather_pooled(k_c, v_c, group)
     if side_stream is not None:
         if k_all is None:
             side_stream.wait_stream(cur)
