@@ -53,7 +53,10 @@ constexpr int kListBytes = 256 * 32 * 8;      // 8 warps x [32 slots][32 lanes] 
 #define S3R_CMP_PEND_SLACK 2
 #endif
 constexpr int kStages = S3R_CMP_STAGES;
-constexpr int kMergeEvery = 4;                // tiles between merges of the pending hits
+#ifndef S3R_CMP_MERGE_EVERY
+#define S3R_CMP_MERGE_EVERY 4
+#endif
+constexpr int kMergeEvery = S3R_CMP_MERGE_EVERY;   // tiles between merges of the pending hits
 constexpr int kOffQ = 0;
 constexpr int kOffK = 2 * kTileBytes;
 constexpr int kOffV = kOffK + kStages * kTileBytes;
