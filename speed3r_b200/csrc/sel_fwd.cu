@@ -31,6 +31,16 @@ namespace s3r {
 #define S3R_SEL16_STAGE_KEYS 32
 #endif
 
+// Larger blocks (32, 64 tokens: not the reference's setting): the same lesson - two CTAs of 8 warps per SM
+// (128 registers, 2-stage rings) run the 64-token kernel in 15.5 ms at 1000 views where one CTA with a 6-stage
+// ring (171 registers) took 22.5 ms.
+#ifndef S3R_SELBIG_STAGES
+#define S3R_SELBIG_STAGES 2
+#endif
+#ifndef S3R_SELBIG_MIN_CTAS
+#define S3R_SELBIG_MIN_CTAS 2
+#endif
+
 template <int BS>
 struct SelCfg {
   static constexpr int kWarps = (BS == 16) ? S3R_SEL16_WARPS : 8;
@@ -39,7 +49,8 @@ struct SelCfg {
   static constexpr int kStageKeys = BS < 32 ? S3R_SEL16_STAGE_KEYS : BS;    // keys per pipeline stage
   static constexpr int kBlkPerStage = kStageKeys / BS;
   static constexpr int kStageBytes = kStageKeys * 128 * 2;  // K tile + V tile
-  static constexpr int kStages = (BS == 16) ? S3R_SEL16_STAGES : 6;
+  static constexpr int kStages = (BS == 16) ? S3R_SEL16_STAGES : S3R_SELBIG_STAGES;
+  static constexpr int kMinCtas = (BS == 16) ? 1 : S3R_SELBIG_MIN_CTAS;
   static constexpr int kQBytes = BS * 128;
   static constexpr int kMaxTopk = 64;
   static constexpr int kSmemBytes = kGroups * (kStages * kStageBytes + kQBytes) + 1024 /*alignment slack*/;
@@ -68,7 +79,7 @@ struct SelParams {
 };
 
 template <int BS>
-__global__ void __launch_bounds__(SelCfg<BS>::kWarps * 32, 1)
+__global__ void __launch_bounds__(SelCfg<BS>::kWarps * 32, SelCfg<BS>::kMinCtas)
 sel_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const SelParams p) {
   using C = SelCfg<BS>;
